@@ -99,6 +99,8 @@ class ModelPlan:
     final_norm: PartSpec
     head: PartSpec
     max_position: int
+    # residual streams per token (hyper-connections); 1: the plain residual stream [T, H]
+    residual_streams: int = 1
 
     def validate(self) -> None:
         n = len(self.layers)

@@ -29,23 +29,30 @@ __device__ __forceinline__ float4 load4f(const __nv_bfloat16* p) {
 __device__ __forceinline__ void store4f(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
 
 // ---------------------------------------------------------------- embedding
+// `copies` > 1: a token's row is written that many times back to back (a model with several
+// residual streams starts them all from the embedded row).
 template <typename WT>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const WT* __restrict__ table,
-                                    float* __restrict__ residual, int H, int vocab) {
+                                    float* __restrict__ residual, int H, int vocab, int copies) {
   pdl_wait();
 
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) id = 0;  // validated on the host; never index outside the table
   const WT* row = table + (size_t)id * H;
-  float* out = residual + (size_t)t * H;
+  float* out = residual + (size_t)t * H * copies;
   // four elements a step where the row allows it (8-byte loads of bfloat16, 16-byte stores)
   if ((H & 3) == 0 && (((uintptr_t)table | (uintptr_t)residual) & 15) == 0 && (H * sizeof(WT)) % 16 == 0) {
-    for (int i = threadIdx.x; i < (H >> 2); i += blockDim.x)
-      *reinterpret_cast<float4*>(out + 4 * i) = load4f(row + 4 * i);
+    for (int i = threadIdx.x; i < (H >> 2); i += blockDim.x) {
+      const float4 v = load4f(row + 4 * i);
+      for (int c = 0; c < copies; ++c) *reinterpret_cast<float4*>(out + (size_t)c * H + 4 * i) = v;
+    }
     return;
   }
-  for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = to_float(row[i]);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = to_float(row[i]);
+    for (int c = 0; c < copies; ++c) out[(size_t)c * H + i] = v;
+  }
 }
 
 // ------------------------------------------------------------------ rmsnorm
@@ -620,10 +627,12 @@ int ft_patch_tokens(int* ids, const int* rows, const int* src, const int* src_in
 }
 
 int ft_embed_gather(const int* ids, const void* table, int table_dtype, float* residual, int T,
-                    int H, int vocab, cudaStream_t stream) {
+                    int H, int vocab, int copies, cudaStream_t stream) {
   if (T <= 0) return FT_OK;
+  if (copies < 1) return FT_ERR_SHAPE;
   FT_DISPATCH(table_dtype, WT,
-              launch_pdl(embed_gather_kernel<WT>, dim3(T), dim3(256), 0, stream, ids, (const WT*)table, residual, H, vocab));
+              launch_pdl(embed_gather_kernel<WT>, dim3(T), dim3(256), 0, stream, ids, (const WT*)table, residual, H, vocab,
+                         copies));
   FT_LAUNCH_CHECK();
   return FT_OK;
 }

@@ -19,7 +19,8 @@ namespace ft {
 __device__ __forceinline__ void select_token(const float* __restrict__ x, const float* __restrict__ bias,
                                              float* score, float* choice, int* ids_out, float* weights_out,
                                              int E, int k, int softmax_scoring, int renormalize, float scale,
-                                             int terms, int lane, int& my_id, float& my_w) {
+                                             int terms, int groups, int keep, int lane, int& my_id,
+                                             float& my_w) {
   // a row holds `terms` partial logits per expert, E apart (the router weight
   // split into bfloat16 terms); they are summed in order, in float32.  A lane takes
   // experts lane, lane + 32, ...; it fetches eight of them at a time into registers
@@ -86,6 +87,53 @@ __device__ __forceinline__ void select_token(const float* __restrict__ x, const 
     }
   }
   __syncwarp();
+  if (groups > 1) {
+    // Experts form `groups` equal groups of neighbours; a group's value is the sum of its two
+    // largest choice values, and only experts of the `keep` best groups stay eligible (the
+    // others count as minus infinity).  Lane l owns groups l, l + 32, ...; the best group is
+    // found `keep` times by a warp-wide argmax (the first of equal groups wins).
+    constexpr int GPL = 8;                     // groups <= 256
+    const int per = E / groups;
+    float gs[GPL];
+    unsigned kept = 0;
+#pragma unroll
+    for (int i = 0; i < GPL; ++i) {
+      const int g = lane + 32 * i;
+      gs[i] = -INFINITY;
+      if (g < groups) {
+        float a = -INFINITY, b = -INFINITY;    // the two largest
+        for (int e = g * per; e < (g + 1) * per; ++e) {
+          const float c = choice[e];
+          if (c > a) { b = a; a = c; }
+          else if (c > b) b = c;
+        }
+        gs[i] = per > 1 ? a + b : a;
+      }
+    }
+    for (int j = 0; j < keep; ++j) {
+      float best = -INFINITY;
+      int arg = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < GPL; ++i) {
+        const int g = lane + 32 * i;
+        if (g < groups && !(kept >> i & 1) && (gs[i] > best || (arg == 0x7fffffff))) { best = gs[i]; arg = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+        if (oa != 0x7fffffff && (arg == 0x7fffffff || ob > best || (ob == best && oa < arg))) { best = ob; arg = oa; }
+      }
+      if (arg != 0x7fffffff && (arg & 31) == lane) kept |= 1u << (arg >> 5);
+    }
+#pragma unroll
+    for (int i = 0; i < GPL; ++i) {
+      const int g = lane + 32 * i;
+      if (g < groups && !(kept >> i & 1))
+        for (int e = g * per; e < (g + 1) * per; ++e) choice[e] = -INFINITY;
+    }
+    __syncwarp();
+  }
   float wsum = 0.f;
   my_id = 0;            // lane j keeps the j-th choice (k <= 32), else it goes through memory
   my_w = 0.f;
@@ -127,7 +175,8 @@ __device__ __forceinline__ void select_token(const float* __restrict__ x, const 
 template <int WARPS>
 __global__ void router_select_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                      int* __restrict__ ids, float* __restrict__ weights, int T, int E,
-                                     int k, int softmax_scoring, int renormalize, float scale, int terms) {
+                                     int k, int softmax_scoring, int renormalize, float scale, int terms,
+                                     int groups, int keep) {
   extern __shared__ float smem[];  // [WARPS][2][E]: scores, choice values
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   pdl_wait();
@@ -138,7 +187,8 @@ __global__ void router_select_kernel(const float* __restrict__ logits, const flo
   int my_id;
   float my_w;
   select_token(logits + (size_t)t * E * terms, bias, score, score + E, ids + (size_t)t * k,
-               weights + (size_t)t * k, E, k, softmax_scoring, renormalize, scale, terms, lane, my_id, my_w);
+               weights + (size_t)t * k, E, k, softmax_scoring, renormalize, scale, terms, groups, keep, lane, my_id,
+               my_w);
   if (k <= 32 && lane < k) {
     ids[(size_t)t * k + lane] = my_id;
     weights[(size_t)t * k + lane] = my_w;
@@ -156,7 +206,7 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32) route_small_kernel(
     const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
     float* __restrict__ weights, int* __restrict__ counts, int* __restrict__ offsets,
     int* __restrict__ sorted_route, int* __restrict__ sorted_token, int* __restrict__ active, int T, int E,
-    int k, int softmax_scoring, int renormalize, float scale, int terms) {
+    int k, int softmax_scoring, int renormalize, float scale, int terms, int groups, int keep) {
   extern __shared__ float smem[];  // [T][2][E] scores and choices, then ints: ids [T*k], counts [E], before [E]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int R = T * k;
@@ -170,7 +220,7 @@ __global__ void __launch_bounds__(SMALL_WARPS * 32) route_small_kernel(
     float my_w;
     float* score = smem + (size_t)warp * 2 * E;
     select_token(logits + (size_t)warp * E * terms, bias, score, score + E, nullptr, nullptr, E, k,
-                 softmax_scoring, renormalize, scale, terms, lane, my_id, my_w);
+                 softmax_scoring, renormalize, scale, terms, groups, keep, lane, my_id, my_w);
     if (lane < k) {
       ids[warp * k + lane] = my_id;
       weights[warp * k + lane] = my_w;
@@ -496,16 +546,18 @@ extern "C" {
 
 int ft_router_select(const float* logits, const float* bias, int* ids, float* weights, int T,
                      int E, int k, int softmax_scoring, int renormalize, float scale, int terms,
-                     cudaStream_t stream) {
+                     int groups, int keep, cudaStream_t stream) {
   if (T <= 0) return FT_OK;
   if (k <= 0 || k > E || terms < 1) return FT_ERR_SHAPE;
+  if (groups < 1 || groups > 256 || E % groups || keep < 1 || keep > groups || keep * (E / groups) < k)
+    return FT_ERR_SHAPE;
   constexpr int WARPS = 4;
   const size_t smem = (size_t)WARPS * 2 * E * sizeof(float);
   if (smem > 200 * 1024) return FT_ERR_SHAPE;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(router_select_kernel<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   launch_pdl(router_select_kernel<WARPS>, dim3((T + WARPS - 1) / WARPS), dim3(WARPS * 32), smem, stream,
-             logits, bias, ids, weights, T, E, k, softmax_scoring, renormalize, scale, terms);
+             logits, bias, ids, weights, T, E, k, softmax_scoring, renormalize, scale, terms, groups, keep);
   FT_LAUNCH_CHECK();
   return FT_OK;
 }
@@ -513,16 +565,19 @@ int ft_router_select(const float* logits, const float* bias, int* ids, float* we
 // router_select + moe_sort in one launch; T <= 8 tokens, k <= 32.
 int ft_route_small(const float* logits, const float* bias, int* ids, float* weights, int* counts,
                    int* offsets, int* sorted_route, int* sorted_token, int* active, int T, int E, int k,
-                   int softmax_scoring, int renormalize, float scale, int terms, cudaStream_t stream) {
+                   int softmax_scoring, int renormalize, float scale, int terms, int groups, int keep,
+                   cudaStream_t stream) {
   if (T <= 0) return FT_OK;
   if (T > SMALL_WARPS || k <= 0 || k > 32 || k > E || terms < 1) return FT_ERR_SHAPE;
+  if (groups < 1 || groups > 256 || E % groups || keep < 1 || keep > groups || keep * (E / groups) < k)
+    return FT_ERR_SHAPE;
   const size_t smem = (size_t)T * 2 * E * sizeof(float) + ((size_t)T * k + 2 * (size_t)E) * sizeof(int);
   if (smem > 160 * 1024) return FT_ERR_SHAPE;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(route_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   launch_pdl(route_small_kernel, dim3(1), dim3(SMALL_WARPS * 32), smem, stream, logits, bias, ids, weights,
              counts, offsets, sorted_route, sorted_token, active, T, E, k, softmax_scoring, renormalize, scale,
-             terms);
+             terms, groups, keep);
   FT_LAUNCH_CHECK();
   return FT_OK;
 }

@@ -101,15 +101,16 @@ def _need_pages(kv_pages: torch.Tensor, dtype) -> None:
 
 # ------------------------------------------------------------------ rows
 def embed_gather(ids: torch.Tensor, table: torch.Tensor, residual: torch.Tensor) -> None:
-    """residual[t,:] = float(table[ids[t],:])"""
+    """residual[t,:] = float(table[ids[t],:]); a ``[T, copies, H]`` residual gets the row ``copies`` times."""
     _need(ids, "ids", torch.int32)
     _need(table, "table")
     _need(residual, "residual", torch.float32)
-    T, H = residual.shape
-    if table.shape[1] != H or ids.numel() != T:
+    T, H = residual.shape[0], residual.shape[-1]
+    copies = residual.shape[1] if residual.dim() == 3 else 1
+    if table.shape[1] != H or ids.numel() != T or residual.dim() not in (2, 3):
         raise KernelError("embed_gather: shapes do not match")
-    f = _fn("elementwise", "ft_embed_gather", "p p i p i i i")
-    _check(f(_ptr(ids), _ptr(table), code(table.dtype), _ptr(residual), T, H, table.shape[0],
+    f = _fn("elementwise", "ft_embed_gather", "p p i p i i i i")
+    _check(f(_ptr(ids), _ptr(table), code(table.dtype), _ptr(residual), T, H, table.shape[0], copies,
              _stream()), "embed_gather")
 
 
@@ -366,15 +367,106 @@ def bias_add(x: torch.Tensor, bias: torch.Tensor) -> None:
     _check(f(_ptr(x), x.stride(0), _ptr(bias), x.shape[0], x.shape[1], code(x.dtype), _stream()), "bias_add")
 
 
-def glu_rows(gate_up: torch.Tensor, mid: torch.Tensor, kind: str) -> None:
-    """mid[t, i] = f(gate_up[t, i]) * gate_up[t, I + i] with ``f`` one of :data:`ACTIVATIONS`."""
+GLU_KINDS = {**ACTIVATIONS, "swigluoai": 3}
+
+
+def glu_rows(gate_up: torch.Tensor, mid: torch.Tensor, kind: str, alpha: float = 1.702, limit: float = 7.0) -> None:
+    """mid[t, i] = f(gate_up[t, i]) * gate_up[t, I + i] with ``f`` one of :data:`ACTIVATIONS`, or the
+    clamped pair ``swigluoai``: ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``,
+    ``g * sigmoid(alpha * g) * (u + 1)``."""
     _need(gate_up, "gate_up")
     _need(mid, "mid", gate_up.dtype)
     T, I = mid.shape
-    if gate_up.shape != (T, 2 * I) or kind not in ACTIVATIONS:
+    if gate_up.shape != (T, 2 * I) or kind not in GLU_KINDS:
         raise KernelError("glu_rows: gate_up must be [T, 2 * I] and the activation a known one")
-    f = _fn("rowwise", "ft_glu_rows", "p p i i i i")
-    _check(f(_ptr(gate_up), _ptr(mid), T, I, ACTIVATIONS[kind], code(mid.dtype), _stream()), "glu_rows")
+    f = _fn("rowwise", "ft_glu_rows", "p p i i i f f i")
+    _check(f(_ptr(gate_up), _ptr(mid), T, I, GLU_KINDS[kind], float(alpha), float(limit), code(mid.dtype),
+             _stream()), "glu_rows")
+
+
+def hyper_norm(streams: torch.Tensor, branch: Optional[torch.Tensor], mix: Optional[torch.Tensor],
+               out_weights: Optional[torch.Tensor], read: Optional[torch.Tensor], weight: torch.Tensor,
+               bias: Optional[torch.Tensor], eps: float, center: bool, normed: Optional[torch.Tensor]) -> None:
+    """Several residual streams per token (``streams`` ``[T, S, H]`` float32, updated in place).  The
+    pending ``branch`` (``[T, H]`` or ``[T, k, H]`` partial rows, summed first) joins them:
+    ``x_t <- sum_s mix[s, t] x_s + out_weights[t] y``; then ``u = sum_s read[s] x_s`` (``read`` None:
+    the plain sum) is layer-normed (``center``: mean taken off; weight and bias) or RMS-normed into
+    ``normed`` (None: only the update)."""
+    _need(streams, "streams", torch.float32)
+    if streams.dim() != 3:
+        raise KernelError("hyper_norm: streams must be [T, S, H]")
+    T, S, H = streams.shape
+    k = 0
+    dtype = normed.dtype if normed is not None else (branch.dtype if branch is not None else torch.float32)
+    if branch is not None:
+        _need(branch, "branch", dtype)
+        k = branch.shape[1] if branch.dim() == 3 else 1
+        _need(mix, "mix", torch.float32)
+        _need(out_weights, "out_weights", torch.float32)
+        if branch.shape[0] != T or branch.shape[-1] != H or mix.shape != (S, S) or out_weights.numel() != S:
+            raise KernelError("hyper_norm: the branch or its connection weights do not fit the streams")
+    for name, t, n in (("read", read, S), ("weight", weight, H), ("bias", bias, H)):
+        if t is not None:
+            _need(t, name, torch.float32)
+            if t.numel() != n:
+                raise KernelError(f"hyper_norm: {name} has the wrong length")
+    if normed is not None:
+        _need(normed, "normed")
+        if normed.shape != (T, H):
+            raise KernelError("hyper_norm: normed must be [T, H]")
+    f = _fn("rowwise", "ft_hyper_norm", "p p i p p p p p f i p i i i i")
+    _check(f(_ptr(streams), _ptr(branch), k, _ptr(mix), _ptr(out_weights), _ptr(read), _ptr(weight), _ptr(bias),
+             float(eps), int(center), _ptr(normed), T, S, H, code(dtype), _stream()), "hyper_norm")
+
+
+def rms_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float) -> None:
+    """out[t, :] = x[t, :] / sqrt(mean(x[t, :]^2) + eps) * weight; ``x`` and ``out`` may be column
+    ranges of wider matrices."""
+    _need(x, "x", contiguous=False)
+    _need(out, "out", x.dtype, contiguous=False)
+    _need(weight, "weight", torch.float32)
+    T, n = x.shape
+    if out.shape != x.shape or weight.numel() != n or x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("rms_rows: shapes do not match")
+    f = _fn("rowwise", "ft_rms_rows", "p q p p q i i f i")
+    _check(f(_ptr(x), x.stride(0), _ptr(weight), _ptr(out), out.stride(0), T, n, float(eps), code(x.dtype),
+             _stream()), "rms_rows")
+
+
+def latent_store(down: torch.Tensor, q: torch.Tensor, q_abs: torch.Tensor, pages: Optional[torch.Tensor],
+                 weight: torch.Tensor, cos_sin: Optional[torch.Tensor], token_pos: torch.Tensor,
+                 token_seg: torch.Tensor, block_table: torch.Tensor, *, heads: int, q_dim: int, rank: int,
+                 rot: int, interleaved: bool, eps: float) -> None:
+    """Latent attention with a rotated key part, between projections and attention.  ``down`` rows are
+    ``[latent (rank) | key part (rot)]``: the latent is RMS-normed times ``weight``, the key part turned
+    by the token's position, both stored as one row ``[rank + rot]`` of ``pages`` (``[pages, 1, page,
+    rank + rot]``; None: nothing is stored).  ``q`` rows hold ``heads`` times ``[q_dim | rot]``: every
+    head's last ``rot`` values are turned and written behind the first ``rank`` values of its row of
+    ``q_abs`` (``[T, heads, rank + rot]``)."""
+    _need(down, "down", contiguous=False)
+    _need(q, "q", down.dtype, contiguous=False)
+    _need(q_abs, "q_abs", down.dtype)
+    _need(weight, "weight", torch.float32)
+    for name, t in (("token_pos", token_pos), ("token_seg", token_seg), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    T = down.shape[0]
+    if down.shape[1] != rank + rot or q.shape != (T, heads * (q_dim + rot)) or down.stride(1) != 1 \
+            or q.stride(1) != 1 or q_abs.shape != (T, heads, rank + rot) or weight.numel() != rank:
+        raise KernelError("latent_store: shapes do not match")
+    if rot:
+        _need(cos_sin, "cos_sin", torch.float32)
+        if cos_sin.shape[1] != rot:
+            raise KernelError("latent_store: the rotation table has the wrong width")
+    P, page_stride = 1, 0
+    if pages is not None:
+        _need(pages, "pages", down.dtype)
+        if pages.dim() != 4 or pages.shape[1] != 1 or pages.shape[3] != rank + rot:
+            raise KernelError("latent_store: pages must be [pages, 1, page, rank + rot]")
+        P, page_stride = pages.shape[2], pages.stride(0)
+    f = _fn("rowwise", "ft_latent_store", "p q p q p p q p p p p p i i i i i i i f i i")
+    _check(f(_ptr(down), down.stride(0), _ptr(q), q.stride(0), _ptr(q_abs), _ptr(pages), page_stride, _ptr(weight),
+             _ptr(cos_sin), _ptr(token_pos), _ptr(token_seg), _ptr(block_table), heads, q_dim, rank, rot, P,
+             block_table.shape[1], int(interleaved), float(eps), code(down.dtype), T, _stream()), "latent_store")
 
 
 # ------------------------------------------------------- mixers with a carried state
@@ -464,22 +556,83 @@ def delta_scan(qkv: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, dt_bi
              _stream()), "delta_scan")
 
 
+def channel_delta_scan(qkv: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, dt_bias: torch.Tensor,
+                       a_log: torch.Tensor, state: torch.Tensor, o: torch.Tensor, seg_slot: torch.Tensor,
+                       seg_q_start: torch.Tensor, heads: int, key_heads: int, key_dim: int, value_dim: int,
+                       unit_eps: float, q_scale: float) -> None:
+    """The gated delta rule with a decay per key channel: as :func:`delta_scan`, but row ``n`` of head
+    ``h``'s state is multiplied by ``exp(-exp(a_log[h]) * softplus(decay[t, h * key_dim + n] + dt_bias[h *
+    key_dim + n]))`` before the token reads and writes.  ``decay`` is float32 ``[T, heads * key_dim]``."""
+    _need(qkv, "qkv", contiguous=False)
+    _need(beta, "beta", qkv.dtype, contiguous=False)
+    _need(decay, "decay", torch.float32, contiguous=False)
+    _need(state, "state", torch.float32, contiguous=False)
+    _need(o, "o", torch.float32)
+    _need(dt_bias, "dt_bias", torch.float32)
+    _need(a_log, "a_log", torch.float32)
+    T = qkv.shape[0]
+    if a_log.numel() != heads or dt_bias.numel() != heads * key_dim:
+        raise KernelError("channel_delta_scan: a_log has one entry per head, dt_bias one per head and key channel")
+    if qkv.shape[1] != 2 * key_heads * key_dim + heads * value_dim or beta.shape != (T, heads) \
+            or decay.shape != (T, heads * key_dim) or o.shape != (T, heads * value_dim) or qkv.stride(1) != 1 \
+            or beta.stride(1) != 1 or decay.stride(1) != 1:
+        raise KernelError("channel_delta_scan: shapes do not match")
+    if state.stride(1) != 1 or state.shape[1] < heads * key_dim * value_dim:
+        raise KernelError("channel_delta_scan: a state row must hold heads * key_dim * value_dim values")
+    f = _fn("recurrent", "ft_channel_delta_scan", "p q p q p q p p p q p p p i i i i f f i i")
+    _check(f(_ptr(qkv), qkv.stride(0), _ptr(beta), beta.stride(0), _ptr(decay), decay.stride(0), _ptr(dt_bias),
+             _ptr(a_log), _ptr(state), state.stride(0), _ptr(o), _ptr(seg_slot), _ptr(seg_q_start), heads, value_dim,
+             key_dim, key_heads, float(unit_eps), float(q_scale), seg_slot.numel(), code(qkv.dtype), _stream()),
+           "channel_delta_scan")
+
+
+def retention_scan(qkv: torch.Tensor, decay: torch.Tensor, cos_sin: Optional[torch.Tensor], seg_pos0: torch.Tensor,
+                   state: torch.Tensor, o: torch.Tensor, seg_slot: torch.Tensor, seg_q_start: torch.Tensor,
+                   heads: int, key_dim: int, value_dim: int, k_scale: float) -> None:
+    """Retention per head: ``S <- decay[h] S + k v^T``, ``o = S^T q``.  ``qkv`` rows are ``q | k | v``
+    (``heads * key_dim`` twice, then ``heads * value_dim``); the first ``cos_sin.shape[1]`` dimensions of
+    every q and k head are turned by the token's position (dimension i with i + half) in float32 and k is
+    multiplied by ``k_scale`` afterwards; ``state`` ``[slots, >= heads * key_dim * value_dim]`` float32."""
+    _need(qkv, "qkv", contiguous=False)
+    _need(decay, "decay", torch.float32)
+    _need(state, "state", torch.float32, contiguous=False)
+    _need(o, "o", torch.float32)
+    _need(seg_pos0, "seg_pos0", torch.int32)
+    T = qkv.shape[0]
+    rot = 0
+    if cos_sin is not None:
+        _need(cos_sin, "cos_sin", torch.float32)
+        rot = cos_sin.shape[1]
+    if decay.numel() != heads or qkv.shape[1] != 2 * heads * key_dim + heads * value_dim \
+            or o.shape != (T, heads * value_dim) or qkv.stride(1) != 1 or rot > key_dim or rot % 2:
+        raise KernelError("retention_scan: shapes do not match")
+    if state.stride(1) != 1 or state.shape[1] < heads * key_dim * value_dim:
+        raise KernelError("retention_scan: a state row must hold heads * key_dim * value_dim values")
+    f = _fn("recurrent", "ft_retention_scan", "p q p p i p p q p p p i i i f i i")
+    _check(f(_ptr(qkv), qkv.stride(0), _ptr(decay), _ptr(cos_sin), rot, _ptr(seg_pos0), _ptr(state), state.stride(0),
+             _ptr(o), _ptr(seg_slot), _ptr(seg_q_start), heads, value_dim, key_dim, float(k_scale),
+             seg_slot.numel(), code(qkv.dtype), _stream()), "retention_scan")
+
+
+GATES = {"silu": 0, "sigmoid": 1}
+
+
 def gated_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, groups: int,
-               eps: float, gate_first: bool) -> None:
+               eps: float, gate_first: bool, gate_kind: str = "silu") -> None:
     """Rows of float32 ``y`` in ``groups`` equal parts, each divided by its own root mean square,
-    times ``weight`` (repeated along the row when shorter); ``silu(gate)`` multiplies the values
-    before the norm (``gate_first``) or the result."""
+    times ``weight`` (repeated along the row when shorter); ``silu(gate)`` (or ``sigmoid(gate)``)
+    multiplies the values before the norm (``gate_first``) or the result."""
     _need(y, "y", torch.float32)
     _need(gate, "gate", out.dtype, contiguous=False)
     _need(weight, "weight", torch.float32)
     _need(out, "out")
     T, width = y.shape
     if gate.shape != y.shape or out.shape != y.shape or gate.stride(1) != 1 or width % groups \
-            or width % weight.numel():
+            or width % weight.numel() or gate_kind not in GATES:
         raise KernelError("gated_norm: shapes do not match")
-    f = _fn("recurrent", "ft_gated_norm", "p p q p i p i i i f i i")
+    f = _fn("recurrent", "ft_gated_norm", "p p q p i p i i i f i i i")
     _check(f(_ptr(y), _ptr(gate), gate.stride(0), _ptr(weight), weight.numel(), _ptr(out), T, width, groups,
-             float(eps), int(gate_first), code(out.dtype), _stream()), "gated_norm")
+             float(eps), int(gate_first), GATES[gate_kind], code(out.dtype), _stream()), "gated_norm")
 
 # ------------------------------------------------------------------ gemm
 def gemm_heads(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> None:
@@ -983,10 +1136,12 @@ def attn_prefill_tc(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
 # ---------------------------------------------------------------- router
 def router_select(logits: torch.Tensor, bias: Optional[torch.Tensor], ids: torch.Tensor,
                   weights: torch.Tensor, k: int, softmax_scoring: bool, renormalize: bool,
-                  scale: float, terms: int = 1) -> None:
+                  scale: float, terms: int = 1, groups: int = 1, keep: int = 1) -> None:
     """Top-k of the scored router logits.  With ``terms`` > 1 a row of ``logits``
     holds that many partial logits per expert (``[T, terms * E]``), summed in
-    order in float32 before scoring."""
+    order in float32 before scoring.  With ``groups`` > 1 the experts form that many equal
+    groups of neighbours, a group's value is the sum of its two largest choice values, and
+    only experts of the ``keep`` best groups can be chosen."""
     _need(logits, "logits", torch.float32)
     _need(ids, "ids", torch.int32)
     _need(weights, "weights", torch.float32)
@@ -995,9 +1150,9 @@ def router_select(logits: torch.Tensor, bias: Optional[torch.Tensor], ids: torch
     T, E = logits.shape[0], logits.shape[1] // terms
     if logits.shape[1] != E * terms or not logits.is_contiguous():
         raise KernelError(f"router_select: logits {tuple(logits.shape)} do not hold {terms} terms per expert")
-    f = _fn("moe_route", "ft_router_select", "p p p p i i i i i f i")
+    f = _fn("moe_route", "ft_router_select", "p p p p i i i i i f i i i")
     _check(f(_ptr(logits), _ptr(bias), _ptr(ids), _ptr(weights), T, E, k, int(softmax_scoring),
-             int(renormalize), float(scale), int(terms), _stream()), "router_select")
+             int(renormalize), float(scale), int(terms), int(groups), int(keep), _stream()), "router_select")
 
 
 ROUTE_SMALL_MAX_T = 8
@@ -1011,7 +1166,8 @@ def route_small_takes(T: int, E: int, k: int) -> bool:
 def route_small(logits: torch.Tensor, bias: Optional[torch.Tensor], ids: torch.Tensor,
                 weights: torch.Tensor, counts: torch.Tensor, offsets: torch.Tensor,
                 sorted_route: torch.Tensor, sorted_token: torch.Tensor, active: torch.Tensor, k: int,
-                softmax_scoring: bool, renormalize: bool, scale: float, terms: int = 1) -> None:
+                softmax_scoring: bool, renormalize: bool, scale: float, terms: int = 1, groups: int = 1,
+                keep: int = 1) -> None:
     """:func:`router_select` and :func:`moe_sort` in one launch (same results)."""
     _need(logits, "logits", torch.float32)
     _need(weights, "weights", torch.float32)
@@ -1027,10 +1183,10 @@ def route_small(logits: torch.Tensor, bias: Optional[torch.Tensor], ids: torch.T
     if counts.numel() < E or offsets.numel() < E + 1 or sorted_route.numel() < R \
             or sorted_token.numel() < R or active.numel() < E + 1 or ids.numel() < R or weights.numel() < R:
         raise KernelError("route_small: output buffers are too small")
-    f = _fn("moe_route", "ft_route_small", "p p p p p p p p p i i i i i f i")
+    f = _fn("moe_route", "ft_route_small", "p p p p p p p p p i i i i i f i i i")
     _check(f(_ptr(logits), _ptr(bias), _ptr(ids), _ptr(weights), _ptr(counts), _ptr(offsets),
              _ptr(sorted_route), _ptr(sorted_token), _ptr(active), T, E, k, int(softmax_scoring),
-             int(renormalize), float(scale), int(terms), _stream()), "route_small")
+             int(renormalize), float(scale), int(terms), int(groups), int(keep), _stream()), "route_small")
 
 
 def router_logits_takes(x: torch.Tensor, w: torch.Tensor) -> bool:

@@ -28,6 +28,11 @@ namespace ft {
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+// a gate's function: 0 silu, 1 sigmoid
+__device__ __forceinline__ float gate_f(float v, int kind) {
+  const float sg = 1.f / (1.f + expf(-v));
+  return kind == 1 ? sg : v * sg;
+}
 
 // Sums V values per lane over the warp with V - 1 + log2(32 / V) shuffles: at every step a lane
 // hands half of its values to the lane `mask` away and adds what it gets to the half it keeps.
@@ -422,9 +427,23 @@ struct DeltaArgs {
   int heads, P, D, G;
   float unit_eps, q_scale;
   int vec;
+  // MODE 1: a decay per key channel
+  const float* decay_rows;   // [T, ld_decay] float32: the decay's projection, channel n of head h at h * D + n;
+  long long ld_decay;        // dt_bias is then [heads * D]
+  // MODE 2: retention
+  const float* cos_sin;      // [positions, rot_dims]: cos | sin (nullptr or rot_dims 0: no rotation)
+  const int* seg_pos0;       // [S]: position of a segment's first token
+  int rot_dims;
 };
 
-template <typename AT, int NPL, int WC>
+// MODE 0: the gated delta rule with one decay per head.
+// MODE 1: the same rule with a decay per key channel: row n of a head's state is multiplied by
+//         g_n = exp(-exp(A_log_h) softplus(a_n + dt_bias[h * D + n])) before the token reads and writes.
+// MODE 2: retention: S <- c_h S + k v^T, o = S^T q with a constant c_h per head (dt_bias[h]), no write
+//         strength and no unit norms; q and k have the first rot_dims dimensions of each head turned
+//         by the token's position (dimension i with i + rot_dims / 2) in shared memory, in float32;
+//         k is multiplied by q_scale after the rotation.
+template <typename AT, int NPL, int WC, int MODE>
 __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(DeltaArgs a) {
   constexpr int COLS = SCAN_WARPS * WC;
   constexpr int NB = (NPL * 32 + SCAN_THREADS - 1) / SCAN_THREADS;
@@ -438,11 +457,22 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(DeltaArgs a) {
   const int col0 = blockIdx.x * COLS;
   const int j0 = col0 + warp * WC;
   const int width = a.heads * P;
-  const int per = SCAN_CHUNK * (2 * D + COLS + 2);
+  const int per = SCAN_CHUNK * ((MODE == 1 ? 3 : 2) * D + COLS + 2);
   const int q0 = a.seg_q_start[seg], q1 = a.seg_q_start[seg + 1];
   float* st = a.state + (size_t)a.seg_slot[seg] * a.slot_stride + (size_t)head * D * P;
-  const float rate = -expf(a.A_log[head]), bias = a.dt_bias[head];
+  const float rate = MODE == 2 ? 0.f : -expf(a.A_log[head]);
+  const float bias = MODE == 1 ? 0.f : a.dt_bias[head];      // MODE 2: the head's constant decay
   const AT* qkv = (const AT*)a.qkv;
+  const int half = MODE == 2 ? a.rot_dims >> 1 : 0;
+  const int pos0 = MODE == 2 && half ? a.seg_pos0[seg] : 0;
+  float ch_bias[NB];                                          // MODE 1: dt_bias of this thread's channels
+  if constexpr (MODE == 1) {
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+      const int n = threadIdx.x + SCAN_THREADS * b;
+      ch_bias[b] = n < D ? a.dt_bias[(size_t)head * D + n] : 0.f;
+    }
+  }
 
   float S[NPL][WC];
 #pragma unroll
@@ -456,6 +486,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(DeltaArgs a) {
   }
 
   AT pq[SCAN_CHUNK][NB], pk[SCAN_CHUNK][NB], pv[XR], pbeta, pdecay;
+  float pg[MODE == 1 ? SCAN_CHUNK : 1][NB];                   // MODE 1: the channels' decay projections
+  float pcos[MODE == 2 ? NPL : 1], psin[MODE == 2 ? NPL : 1]; // MODE 2: pair (tt, i) = threadIdx.x + 128 r
   auto fetch = [&](int t0, int nt) {
 #pragma unroll
     for (int tt = 0; tt < SCAN_CHUNK; ++tt) {
@@ -466,6 +498,19 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(DeltaArgs a) {
           const AT* row = qkv + (size_t)(t0 + tt) * a.ld + (size_t)g * D + n;
           pq[tt][b] = row[0];
           pk[tt][b] = row[(size_t)a.G * D];
+          if constexpr (MODE == 1) pg[tt][b] = a.decay_rows[(size_t)(t0 + tt) * a.ld_decay + (size_t)head * D + n];
+        }
+      }
+    }
+    if constexpr (MODE == 2) {
+#pragma unroll
+      for (int r = 0; r < NPL; ++r) {
+        const int idx = threadIdx.x + SCAN_THREADS * r;
+        if (half && idx < nt * half) {
+          const int tt = idx / half, i = idx - tt * half;
+          const float* cs = a.cos_sin + (size_t)(pos0 + t0 + tt - q0) * a.rot_dims;
+          pcos[r] = cs[i];
+          psin[r] = cs[half + i];
         }
       }
     }
@@ -476,10 +521,10 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(DeltaArgs a) {
                   ? qkv[(size_t)(t0 + tt) * a.ld + 2 * (size_t)a.G * D + (size_t)head * P + col0 + c]
                   : from_float<AT>(0.f);
     }
-    if ((int)threadIdx.x < nt) {
+    if (MODE != 2 && (int)threadIdx.x < nt) {
       const size_t at = (size_t)(t0 + threadIdx.x) * a.ld_gate + head;
       pbeta = ((const AT*)a.beta)[at];
-      pdecay = ((const AT*)a.decay)[at];
+      if constexpr (MODE == 0) pdecay = ((const AT*)a.decay)[at];
     }
   };
   auto put = [&](float* buf, int nt) {
@@ -495,6 +540,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(DeltaArgs a) {
         if (tt < nt && n < D) {
           qs[tt * D + n] = to_float(pq[tt][b]);
           ks[tt * D + n] = to_float(pk[tt][b]);
+          if constexpr (MODE == 1)
+            gates[2 * SCAN_CHUNK + tt * D + n] = expf(rate * softplus_f(pg[tt][b] + ch_bias[b]));
         }
       }
     }
@@ -504,13 +551,44 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(DeltaArgs a) {
       if (i < SCAN_CHUNK * COLS) vs[i] = to_float(pv[r]);
     }
     if ((int)threadIdx.x < nt) {
-      gates[threadIdx.x] = 1.f / (1.f + expf(-to_float(pbeta)));
-      gates[SCAN_CHUNK + threadIdx.x] = expf(rate * softplus_f(to_float(pdecay) + bias));
+      if constexpr (MODE == 2) {
+        gates[threadIdx.x] = 1.f;
+        gates[SCAN_CHUNK + threadIdx.x] = bias;
+      } else {
+        gates[threadIdx.x] = 1.f / (1.f + expf(-to_float(pbeta)));
+        gates[SCAN_CHUNK + threadIdx.x] = MODE == 1 ? 1.f : expf(rate * softplus_f(to_float(pdecay) + bias));
+      }
+    }
+  };
+  // MODE 2: turn the staged q and k rows of a chunk; a thread owns whole pairs
+  auto turn_rows = [&](float* buf, int nt) {
+    if constexpr (MODE == 2) {
+      float* qs = buf;
+      float* ks = qs + SCAN_CHUNK * D;
+#pragma unroll
+      for (int r = 0; r < NPL; ++r) {
+        const int idx = threadIdx.x + SCAN_THREADS * r;
+        if (half && idx < nt * half) {
+          const int tt = idx / half, i = idx - tt * half;
+          const float c = pcos[r], sn = psin[r];
+          float* qa = qs + tt * D + i;
+          float* ka = ks + tt * D + i;
+          const float qu = qa[0], qv = qa[half], ku = ka[0], kv_ = ka[half];
+          qa[0] = qu * c - qv * sn;
+          qa[half] = qv * c + qu * sn;
+          ka[0] = ku * c - kv_ * sn;
+          ka[half] = kv_ * c + ku * sn;
+        }
+      }
     }
   };
 
   fetch(q0, min(SCAN_CHUNK, q1 - q0));
   put(sm, min(SCAN_CHUNK, q1 - q0));
+  if constexpr (MODE == 2) {
+    __syncthreads();
+    turn_rows(sm, min(SCAN_CHUNK, q1 - q0));
+  }
   __syncthreads();
   int turn = 0;
   for (int t0 = q0; t0 < q1; t0 += SCAN_CHUNK, turn ^= 1) {
@@ -532,19 +610,35 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(DeltaArgs a) {
         const int n = lane + 32 * e;
         qv[e] = n < D ? qs[tt * D + n] : 0.f;
         kv[e] = n < D ? ks[tt * D + n] : 0.f;
+        if constexpr (MODE == 2) kv[e] *= a.q_scale;
         unit[0] = fmaf(qv[e], qv[e], unit[0]);
         unit[1] = fmaf(kv[e], kv[e], unit[1]);
         unit[2] = fmaf(qv[e], kv[e], unit[2]);
       }
       warp_sum_multi<4>(unit);
       const float mine_u = unit[0];                       // lane l holds value l >> 3
-      const float iq = a.q_scale / sqrtf(__shfl_sync(0xffffffffu, mine_u, 0) + a.unit_eps);
-      const float ik = 1.f / sqrtf(__shfl_sync(0xffffffffu, mine_u, 8) + a.unit_eps);
-      const float kq = __shfl_sync(0xffffffffu, mine_u, 16) * iq * ik;
+      float kq;
+      if constexpr (MODE == 2) {
+        kq = __shfl_sync(0xffffffffu, mine_u, 16);
+      } else {
+        const float iq = a.q_scale / sqrtf(__shfl_sync(0xffffffffu, mine_u, 0) + a.unit_eps);
+        const float ik = 1.f / sqrtf(__shfl_sync(0xffffffffu, mine_u, 8) + a.unit_eps);
+        kq = __shfl_sync(0xffffffffu, mine_u, 16) * iq * ik;
 #pragma unroll
-      for (int e = 0; e < NPL; ++e) {
-        qv[e] *= iq;
-        kv[e] *= ik;
+        for (int e = 0; e < NPL; ++e) {
+          qv[e] *= iq;
+          kv[e] *= ik;
+        }
+      }
+      if constexpr (MODE == 1) {
+        // every row of the state decays by its own channel's factor before the token reads it
+#pragma unroll
+        for (int e = 0; e < NPL; ++e) {
+          const int n = lane + 32 * e;
+          const float gn = n < D ? gates[2 * SCAN_CHUNK + tt * D + n] : 1.f;
+#pragma unroll
+          for (int c = 0; c < WC; ++c) S[e][c] *= gn;
+        }
       }
       // per column: S^T k and S^T q of the state before this token
       float red[2 * WC];
@@ -569,7 +663,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(DeltaArgs a) {
         const float v = vs[tt * COLS + warp * WC + c];
         // the decayed state answers k with decay * sa; the token writes u along k, and its own
         // read-out already contains that write: decay * sb + (k . q) u
-        const float u = beta * (v - decay * sa);
+        const float u = MODE == 2 ? v : beta * (v - decay * sa);
         if (lane == 0 && j0 + c < P)
           a.o[(size_t)(t0 + tt) * width + (size_t)head * P + j0 + c] = fmaf(kq, u, decay * sb);
 #pragma unroll
@@ -583,6 +677,12 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(DeltaArgs a) {
       for (int tt = 0; tt < nt; ++tt) token(tt);
     }
     if (next > 0) put(sm + (turn ^ 1) * per, next);
+    if constexpr (MODE == 2) {
+      if (next > 0) {
+        __syncthreads();
+        turn_rows(sm + (turn ^ 1) * per, next);
+      }
+    }
     __syncthreads();
   }
 #pragma unroll
@@ -594,13 +694,13 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(DeltaArgs a) {
 
 // --------------------------------------------------------------------- gated norm
 // A row of `width` float32 values in `groups` equal parts, each divided by its own root mean
-// square; times weight[i % weight_len]; a gate silu(z) on the values before the norm
+// square; times weight[i % weight_len]; a gate silu(z) (or sigmoid(z)) on the values before the norm
 // (gate_first) or on the result.  One warp per (token, group).
 template <typename AT>
 __global__ void __launch_bounds__(128) gated_norm_kernel(const float* __restrict__ y, const AT* __restrict__ z,
                                                          long long ldz, const float* __restrict__ weight,
                                                          int weight_len, AT* __restrict__ out, int T, int width,
-                                                         int groups, float eps, int gate_first) {
+                                                         int groups, float eps, int gate_first, int gate_kind) {
   pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -612,13 +712,13 @@ __global__ void __launch_bounds__(128) gated_norm_kernel(const float* __restrict
   float ss = 0.f;
   for (int i = lane; i < size; i += 32) {
     float v = row[i];
-    if (gate_first) v *= silu_f(to_float(gate[i]));
+    if (gate_first) v *= gate_f(to_float(gate[i]), gate_kind);
     ss = fmaf(v, v, ss);
   }
   const float inv = 1.f / sqrtf(warp_sum(ss) / (float)size + eps);
   AT* dst = out + (size_t)t * width + base;
   for (int i = lane; i < size; i += 32) {
-    const float gv = silu_f(to_float(gate[i]));
+    const float gv = gate_f(to_float(gate[i]), gate_kind);
     float v = row[i];
     if (gate_first) v *= gv;
     v = v * inv * weight[(base + i) % weight_len];
@@ -649,7 +749,7 @@ template <typename AT, int TPI, int KEEP>
 __global__ void __launch_bounds__(128) gated_norm_vec_kernel(const float* __restrict__ y, const AT* __restrict__ z,
                                                              long long ldz, const float* __restrict__ weight,
                                                              int weight_len, AT* __restrict__ out, int T, int width,
-                                                             int groups, float eps, int gate_first) {
+                                                             int groups, float eps, int gate_first, int gate_kind) {
   __shared__ float scratch[33];
   pdl_wait();
   const int sub = threadIdx.x % TPI;
@@ -667,7 +767,7 @@ __global__ void __launch_bounds__(128) gated_norm_vec_kernel(const float* __rest
     if (gi < pieces) {
       float4 v = ld4(row + 4 * gi);
       const float4 gr = ld4(gate + 4 * gi);
-      const float4 gv = make_float4(silu_f(gr.x), silu_f(gr.y), silu_f(gr.z), silu_f(gr.w));
+      const float4 gv = make_float4(gate_f(gr.x, gate_kind), gate_f(gr.y, gate_kind), gate_f(gr.z, gate_kind), gate_f(gr.w, gate_kind));
       if (gate_first) { v.x *= gv.x; v.y *= gv.y; v.z *= gv.z; v.w *= gv.w; }
       keep[j] = v;
       gk[j] = gv;
@@ -712,15 +812,33 @@ static int launch_ssd(SsdArgs a, int S, cudaStream_t stream) {
   return e == cudaSuccess ? FT_OK : (int)e;
 }
 
-template <typename AT, int NPL, int WC>
+template <typename AT, int NPL, int WC, int MODE = 0>
 static int launch_delta(DeltaArgs a, int S, cudaStream_t stream) {
   constexpr int COLS = SCAN_WARPS * WC;
-  const size_t smem = (size_t)2 * SCAN_CHUNK * (2 * a.D + COLS + 2) * sizeof(float);
-  if (smem > 48 * 1024) return FT_ERR_SHAPE;
+  const size_t smem = (size_t)2 * SCAN_CHUNK * ((MODE == 1 ? 3 : 2) * a.D + COLS + 2) * sizeof(float);
+  if (smem > 96 * 1024) return FT_ERR_SHAPE;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(delta_scan_kernel<AT, NPL, WC, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   a.vec = !(a.P % (WC % 4 == 0 ? 4 : 2)) && !(a.slot_stride % 4) && !((uintptr_t)a.state & 15);
   const dim3 grid((a.P + COLS - 1) / COLS, a.heads, S);
-  cudaError_t e = launch_pdl(delta_scan_kernel<AT, NPL, WC>, grid, dim3(SCAN_THREADS), smem, stream, a);
+  cudaError_t e = launch_pdl(delta_scan_kernel<AT, NPL, WC, MODE>, grid, dim3(SCAN_THREADS), smem, stream, a);
   return e == cudaSuccess ? FT_OK : (int)e;
+}
+
+template <int MODE>
+static int dispatch_delta(DeltaArgs a, int S, int dtype, cudaStream_t stream) {
+  int rc = FT_OK;
+  const int D = a.D;
+  const bool narrow = narrow_warps(a.P, a.heads, S);
+  FT_DISPATCH(dtype, AT, {
+    if (D <= 32) rc = narrow ? launch_delta<AT, 1, NARROW_WC, MODE>(a, S, stream) : launch_delta<AT, 1, 8, MODE>(a, S, stream);
+    else if (D <= 64) rc = narrow ? launch_delta<AT, 2, NARROW_WC, MODE>(a, S, stream) : launch_delta<AT, 2, 8, MODE>(a, S, stream);
+    else if (D <= 128) rc = narrow ? launch_delta<AT, 4, NARROW_WC, MODE>(a, S, stream) : launch_delta<AT, 4, 8, MODE>(a, S, stream);
+    else rc = narrow ? launch_delta<AT, 8, NARROW_WC, MODE>(a, S, stream) : launch_delta<AT, 8, 8, MODE>(a, S, stream);
+  });
+  if (rc != FT_OK) return rc;
+  FT_LAUNCH_CHECK();
+  return FT_OK;
 }
 
 }  // namespace ft
@@ -790,22 +908,41 @@ int ft_delta_scan(const void* qkv, long long ld, const void* beta, const void* d
   if (S <= 0) return FT_OK;
   if (heads <= 0 || P <= 0 || D <= 0 || D > 256 || G <= 0 || heads % G) return FT_ERR_SHAPE;
   DeltaArgs a{qkv, beta, decay, dt_bias, A_log, state, o, seg_slot, seg_q_start, ld, ld_gate, slot_stride,
-              heads, P, D, G, unit_eps, q_scale, 0};
-  int rc = FT_OK;
-  const bool narrow = narrow_warps(P, heads, S);
-  FT_DISPATCH(dtype, AT, {
-    if (D <= 32) rc = narrow ? launch_delta<AT, 1, NARROW_WC>(a, S, stream) : launch_delta<AT, 1, 8>(a, S, stream);
-    else if (D <= 64) rc = narrow ? launch_delta<AT, 2, NARROW_WC>(a, S, stream) : launch_delta<AT, 2, 8>(a, S, stream);
-    else if (D <= 128) rc = narrow ? launch_delta<AT, 4, NARROW_WC>(a, S, stream) : launch_delta<AT, 4, 8>(a, S, stream);
-    else rc = narrow ? launch_delta<AT, 8, NARROW_WC>(a, S, stream) : launch_delta<AT, 8, 8>(a, S, stream);
-  });
-  if (rc != FT_OK) return rc;
-  FT_LAUNCH_CHECK();
-  return FT_OK;
+              heads, P, D, G, unit_eps, q_scale, 0, nullptr, 0, nullptr, nullptr, 0};
+  return dispatch_delta<0>(a, S, dtype, stream);
+}
+
+// The delta rule with a decay per key channel: `decay` is float32 [T, ld_decay] (channel n of head
+// h at column h * D + n), dt_bias [heads * D].
+int ft_channel_delta_scan(const void* qkv, long long ld, const void* beta, long long ld_gate, const float* decay,
+                          long long ld_decay, const float* dt_bias, const float* A_log, float* state,
+                          long long slot_stride, float* o, const int* seg_slot, const int* seg_q_start, int heads,
+                          int P, int D, int G, float unit_eps, float q_scale, int S, int dtype,
+                          cudaStream_t stream) {
+  if (S <= 0) return FT_OK;
+  if (heads <= 0 || P <= 0 || D <= 0 || D > 256 || G <= 0 || heads % G) return FT_ERR_SHAPE;
+  DeltaArgs a{qkv, beta, nullptr, dt_bias, A_log, state, o, seg_slot, seg_q_start, ld, ld_gate, slot_stride,
+              heads, P, D, G, unit_eps, q_scale, 0, decay, ld_decay, nullptr, nullptr, 0};
+  return dispatch_delta<1>(a, S, dtype, stream);
+}
+
+// Retention: rows of `qkv` are q (heads * D) | k (heads * D) | v (heads * P); `decay` [heads] float32 holds
+// each head's constant factor; cos_sin [positions, rot_dims] (rot_dims 0: nothing turns).
+int ft_retention_scan(const void* qkv, long long ld, const float* decay, const float* cos_sin, int rot_dims,
+                      const int* seg_pos0, float* state, long long slot_stride, float* o, const int* seg_slot,
+                      const int* seg_q_start, int heads, int P, int D, float k_scale, int S, int dtype,
+                      cudaStream_t stream) {
+  if (S <= 0) return FT_OK;
+  if (heads <= 0 || P <= 0 || D <= 0 || D > 256 || rot_dims < 0 || (rot_dims & 1) || rot_dims > D)
+    return FT_ERR_SHAPE;
+  DeltaArgs a{qkv, nullptr, nullptr, decay, nullptr, state, o, seg_slot, seg_q_start, ld, 0, slot_stride,
+              heads, P, D, heads, 0.f, k_scale, 0, nullptr, 0, cos_sin, seg_pos0, cos_sin ? rot_dims : 0};
+  return dispatch_delta<2>(a, S, dtype, stream);
 }
 
 int ft_gated_norm(const float* y, const void* z, long long ldz, const float* weight, int weight_len, void* out,
-                  int T, int width, int groups, float eps, int gate_first, int dtype, cudaStream_t stream) {
+                  int T, int width, int groups, float eps, int gate_first, int gate_kind, int dtype,
+                  cudaStream_t stream) {
   if (T <= 0) return FT_OK;
   if (width <= 0 || groups <= 0 || width % groups || weight_len <= 0) return FT_ERR_SHAPE;
   const long long items = (long long)T * groups;
@@ -815,27 +952,27 @@ int ft_gated_norm(const float* y, const void* z, long long ldz, const float* wei
   if (vec && size <= 16 * 32) {
     FT_DISPATCH(dtype, AT, launch_pdl(gated_norm_vec_kernel<AT, 32, 4>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream,
                                       y, (const AT*)z, ldz, weight, weight_len, (AT*)out, T, width, groups, eps,
-                                      gate_first));
+                                      gate_first, gate_kind));
     FT_LAUNCH_CHECK();
     return FT_OK;
   }
   if (vec && size <= 16 * 128) {
     FT_DISPATCH(dtype, AT, launch_pdl(gated_norm_vec_kernel<AT, 128, 4>, dim3((unsigned)items), dim3(128), 0, stream, y,
                                       (const AT*)z, ldz, weight, weight_len, (AT*)out, T, width, groups, eps,
-                                      gate_first));
+                                      gate_first, gate_kind));
     FT_LAUNCH_CHECK();
     return FT_OK;
   }
   if (vec && size <= 64 * 128) {
     FT_DISPATCH(dtype, AT, launch_pdl(gated_norm_vec_kernel<AT, 128, 16>, dim3((unsigned)items), dim3(128), 0, stream, y,
                                       (const AT*)z, ldz, weight, weight_len, (AT*)out, T, width, groups, eps,
-                                      gate_first));
+                                      gate_first, gate_kind));
     FT_LAUNCH_CHECK();
     return FT_OK;
   }
   const unsigned blocks = (unsigned)((items + 3) / 4);
   FT_DISPATCH(dtype, AT, launch_pdl(gated_norm_kernel<AT>, dim3(blocks), dim3(128), 0, stream, y, (const AT*)z, ldz,
-                                    weight, weight_len, (AT*)out, T, width, groups, eps, gate_first));
+                                    weight, weight_len, (AT*)out, T, width, groups, eps, gate_first, gate_kind));
   FT_LAUNCH_CHECK();
   return FT_OK;
 }

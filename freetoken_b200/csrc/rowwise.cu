@@ -400,16 +400,177 @@ bias_add_kernel(AT* __restrict__ x, long long ld, const float* __restrict__ bias
 }
 
 // mid[t, i] = f(gu[t, i]) * gu[t, I + i]: the gate and up halves of one merged projection
+// kind 3: the clamped pair  g = min(gate, limit), u = clamp(up, -limit, limit),  g sigmoid(alpha g) (u + 1)
 template <typename AT>
 __global__ void __launch_bounds__(256)
-glu_rows_kernel(const AT* __restrict__ gu, AT* __restrict__ mid, long long n, int I, int kind) {
+glu_rows_kernel(const AT* __restrict__ gu, AT* __restrict__ mid, long long n, int I, int kind, float alpha,
+                float limit) {
   pdl_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const long long t = i / I;
   const int c = (int)(i - t * I);
   const AT* row = gu + (size_t)t * 2 * I;
-  mid[i] = from_float<AT>(act_apply(to_float(row[c]), kind) * to_float(row[I + c]));
+  const float gate = to_float(row[c]), up = to_float(row[I + c]);
+  float v;
+  if (kind == 3) {
+    const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+    v = g / (1.f + expf(-alpha * g)) * (u + 1.f);
+  } else {
+    v = act_apply(gate, kind) * up;
+  }
+  mid[i] = from_float<AT>(v);
+}
+
+// ------------------------------------------------- several residual streams (hyper-connections)
+// A token has S residual streams x_0 .. x_{S-1} (float32, [T, S, H]).  One launch, per token:
+//   1. the pending branch output y (the sum of its k partial rows, ascending) joins the streams:
+//        x_t <- sum_s mix[s, t] x_s + out[t] y          (all t from the old x; skipped without a branch)
+//   2. the next sublayer's input  u = sum_s read[s] x_s   (read == nullptr: the plain sum)
+//   3. layer norm (mean, then the mean of the squared deviations, eps inside the root, weight and
+//      bias) or RMS norm (no bias) of u into `normed` in the activation type.
+// One block per token; u is kept in shared memory between the passes; every sum has a fixed order.
+constexpr int HYPER_MAX_STREAMS = 8;
+template <typename AT>
+__global__ void __launch_bounds__(256)
+hyper_norm_kernel(float* __restrict__ streams, const AT* __restrict__ branch, int k, const float* __restrict__ mix,
+                  const float* __restrict__ out_w, const float* __restrict__ read, const float* __restrict__ weight,
+                  const float* __restrict__ bias, float eps, int center, AT* __restrict__ normed, int S, int H) {
+  extern __shared__ float u_row[];
+  __shared__ float scratch[33];
+  __shared__ float s_mix[HYPER_MAX_STREAMS * HYPER_MAX_STREAMS], s_out[HYPER_MAX_STREAMS], s_read[HYPER_MAX_STREAMS];
+  pdl_wait();
+  const int t = blockIdx.x;
+  if (threadIdx.x < S * S) s_mix[threadIdx.x] = branch ? mix[threadIdx.x] : 0.f;
+  if (threadIdx.x < S) {
+    s_out[threadIdx.x] = branch ? out_w[threadIdx.x] : 0.f;
+    s_read[threadIdx.x] = read ? read[threadIdx.x] : 1.f;
+  }
+  __syncthreads();
+  float* x = streams + (size_t)t * S * H;
+  const AT* y_rows = branch ? branch + (size_t)t * k * H : nullptr;
+  float sum = 0.f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    float xs[HYPER_MAX_STREAMS];
+#pragma unroll
+    for (int s = 0; s < HYPER_MAX_STREAMS; ++s) xs[s] = s < S ? x[(size_t)s * H + c] : 0.f;
+    if (branch) {
+      float y = 0.f;
+      for (int j = 0; j < k; ++j) y += to_float(y_rows[(size_t)j * H + c]);
+      float nx[HYPER_MAX_STREAMS];
+#pragma unroll
+      for (int r = 0; r < HYPER_MAX_STREAMS; ++r) {
+        float v = 0.f;
+        if (r < S) {
+#pragma unroll
+          for (int s = 0; s < HYPER_MAX_STREAMS; ++s)
+            if (s < S) v = fmaf(s_mix[s * S + r], xs[s], v);
+          v = fmaf(s_out[r], y, v);
+          x[(size_t)r * H + c] = v;
+        }
+        nx[r] = v;
+      }
+#pragma unroll
+      for (int s = 0; s < HYPER_MAX_STREAMS; ++s) xs[s] = nx[s];
+    }
+    float u = 0.f;
+#pragma unroll
+    for (int s = 0; s < HYPER_MAX_STREAMS; ++s)
+      if (s < S) u = fmaf(s_read[s], xs[s], u);
+    u_row[c] = u;
+    sum += u;
+  }
+  if (!normed) return;
+  float mean = 0.f;
+  if (center) mean = block_sum(sum, scratch) / (float)H;
+  float sq = 0.f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    const float d = u_row[c] - mean;
+    sq = fmaf(d, d, sq);
+  }
+  const float inv = 1.f / sqrtf(block_sum(sq, scratch) / (float)H + eps);
+  AT* dst = normed + (size_t)t * H;
+  for (int c = threadIdx.x; c < H; c += blockDim.x)
+    dst[c] = from_float<AT>((u_row[c] - mean) * inv * weight[c] + (bias ? bias[c] : 0.f));
+}
+
+// Rows of a column range of a wider matrix, RMS-normed and multiplied by a weight:
+// out[t, :] = x[t, :] / sqrt(mean(x[t, :]^2) + eps) * w.   One block per row.
+template <typename AT>
+__global__ void __launch_bounds__(128)
+rms_rows_kernel(const AT* __restrict__ x, long long ldx, const float* __restrict__ w, AT* __restrict__ out,
+                long long ldo, int n, float eps) {
+  __shared__ float scratch[33];
+  pdl_wait();
+  const AT* row = x + (size_t)blockIdx.x * ldx;
+  float sq = 0.f;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    const float v = to_float(row[c]);
+    sq = fmaf(v, v, sq);
+  }
+  const float inv = 1.f / sqrtf(block_sum(sq, scratch) / (float)n + eps);
+  AT* dst = out + (size_t)blockIdx.x * ldo;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) dst[c] = from_float<AT>(to_float(row[c]) * inv * w[c]);
+}
+
+// What latent attention with a rotated key part does between its projections and its attention.
+// Per token: the latent (rank values of the down projection's row) is RMS-normed, times its weight,
+// and stored in the token's place of the page; the rot values behind it are turned by the token's
+// position (dimension 2i with 2i + 1, or i with i + rot/2) and stored behind the latent: a cached
+// row is [latent | rotated key part].  The rotated part of every head's query (the last rot of its
+// dq + rot values) is turned the same way and written behind the first rank values of the head's
+// row of q_abs ([T, heads, rank + rot]), whose first rank values another product fills.
+struct LatentStoreArgs {
+  const void* down;        // [T, ld_down]: latent at column 0, the key part to rotate at column rank
+  const void* q;           // [T, ld_q]: head h at column h * (dq + rot)
+  void* q_abs;             // [T, heads, rank + rot]
+  void* pages;             // [pages, 1, P, rank + rot] or nullptr
+  const float* weight;     // [rank]
+  const float* cos_sin;    // [positions, rot]: cos | sin
+  const int* token_pos;
+  const int* token_seg;
+  const int* block_table;  // [segments, table_width]
+  long long ld_down, ld_q, page_stride;
+  int heads, dq, rank, rot, P, table_width, interleaved;
+  float eps;
+};
+
+template <typename AT>
+__global__ void __launch_bounds__(128) latent_store_kernel(LatentStoreArgs a) {
+  __shared__ float scratch[33];
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int pos = a.token_pos[t];
+  const int half = a.rot >> 1;
+  const float* cs = a.cos_sin + (size_t)pos * a.rot;
+  auto turn = [&](const AT* src, AT* dst, int i) {       // pair i of a rotated part
+    const int ia = a.interleaved ? 2 * i : i, ib = a.interleaved ? 2 * i + 1 : i + half;
+    const float u = to_float(src[ia]), v = to_float(src[ib]);
+    const float c = cs[i], s = cs[half + i];
+    dst[ia] = from_float<AT>(u * c - v * s);
+    dst[ib] = from_float<AT>(v * c + u * s);
+  };
+  const int width = a.rank + a.rot;
+  // queries: the rotated part of every head
+  const AT* q = (const AT*)a.q + (size_t)t * a.ld_q;
+  AT* qa = (AT*)a.q_abs + (size_t)t * a.heads * width;
+  for (int i = threadIdx.x; i < a.heads * half; i += blockDim.x) {
+    const int h = i / half, p = i - h * half;
+    turn(q + (size_t)h * (a.dq + a.rot) + a.dq, qa + (size_t)h * width + a.rank, p);
+  }
+  if (!a.pages) return;
+  const AT* down = (const AT*)a.down + (size_t)t * a.ld_down;
+  const int page = a.block_table[(size_t)a.token_seg[t] * a.table_width + pos / a.P];
+  AT* dst = (AT*)a.pages + (size_t)page * a.page_stride + (size_t)(pos % a.P) * width;
+  float sq = 0.f;
+  for (int c = threadIdx.x; c < a.rank; c += blockDim.x) {
+    const float v = to_float(down[c]);
+    sq = fmaf(v, v, sq);
+  }
+  const float inv = 1.f / sqrtf(block_sum(sq, scratch) / (float)a.rank + a.eps);
+  for (int c = threadIdx.x; c < a.rank; c += blockDim.x)
+    dst[c] = from_float<AT>(to_float(down[c]) * inv * a.weight[c]);
+  for (int i = threadIdx.x; i < half; i += blockDim.x) turn(down + a.rank, dst + a.rank, i);
 }
 
 }  // namespace ft
@@ -546,13 +707,50 @@ int ft_bias_add(void* x, long long ld, const float* bias, int T, int width, int 
   return FT_OK;
 }
 
-int ft_glu_rows(const void* gu, void* mid, int T, int I, int kind, int dtype, cudaStream_t stream) {
+int ft_glu_rows(const void* gu, void* mid, int T, int I, int kind, float alpha, float limit, int dtype,
+                cudaStream_t stream) {
   if (T <= 0 || I <= 0) return FT_OK;
-  if (kind < 0 || kind > 2) return FT_ERR_SHAPE;
+  if (kind < 0 || kind > 3) return FT_ERR_SHAPE;
   const long long n = (long long)T * I;
   FT_DISPATCH(dtype, AT,
               (launch_pdl(glu_rows_kernel<AT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream,
-                          (const AT*)gu, (AT*)mid, n, I, kind)));
+                          (const AT*)gu, (AT*)mid, n, I, kind, alpha, limit)));
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+int ft_hyper_norm(float* streams, const void* branch, int k, const float* mix, const float* out_w,
+                  const float* read, const float* weight, const float* bias, float eps, int center, void* normed,
+                  int T, int S, int H, int dtype, cudaStream_t stream) {
+  if (T <= 0) return FT_OK;
+  if (S < 1 || S > HYPER_MAX_STREAMS || H <= 0 || H > 10240 || (branch && k <= 0)) return FT_ERR_SHAPE;
+  FT_DISPATCH(dtype, AT,
+              (launch_pdl(hyper_norm_kernel<AT>, dim3(T), dim3(256), (size_t)H * sizeof(float), stream, streams,
+                          (const AT*)branch, k, mix, out_w, read, weight, bias, eps, center, (AT*)normed, S, H)));
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+int ft_rms_rows(const void* x, long long ldx, const float* w, void* out, long long ldo, int T, int n, float eps,
+                int dtype, cudaStream_t stream) {
+  if (T <= 0) return FT_OK;
+  if (n <= 0) return FT_ERR_SHAPE;
+  FT_DISPATCH(dtype, AT,
+              (launch_pdl(rms_rows_kernel<AT>, dim3(T), dim3(128), 0, stream, (const AT*)x, ldx, w, (AT*)out, ldo, n,
+                          eps)));
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
+
+int ft_latent_store(const void* down, long long ld_down, const void* q, long long ld_q, void* q_abs, void* pages,
+                    long long page_stride, const float* weight, const float* cos_sin, const int* token_pos,
+                    const int* token_seg, const int* block_table, int heads, int dq, int rank, int rot, int P,
+                    int table_width, int interleaved, float eps, int dtype, int T, cudaStream_t stream) {
+  if (T <= 0) return FT_OK;
+  if (heads <= 0 || dq < 0 || rank <= 0 || rot < 0 || (rot & 1) || P <= 0) return FT_ERR_SHAPE;
+  LatentStoreArgs a{down, q, q_abs, pages, weight, cos_sin, token_pos, token_seg, block_table, ld_down, ld_q,
+                    page_stride, heads, dq, rank, rot, P, table_width, interleaved, eps};
+  FT_DISPATCH(dtype, AT, (launch_pdl(latent_store_kernel<AT>, dim3(T), dim3(128), 0, stream, a)));
   FT_LAUNCH_CHECK();
   return FT_OK;
 }

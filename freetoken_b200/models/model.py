@@ -139,7 +139,9 @@ class Model:
         that ``logit_rows`` is ``0..T-1``, which saves the row gather."""
         T = ctx.num_tokens
         H = self.plan.hidden_size
-        residual = ctx.workspace.get("model.residual", (T, H), torch.float32)
+        streams = self.plan.residual_streams
+        # several residual streams per token start out as copies of the embedded row
+        residual = ctx.workspace.get("model.residual", (T, H) if streams == 1 else (T, streams, H), torch.float32)
         self.embedding.forward(ctx, residual)
         delta = None
         for stop, cache in zip(self.plan.schedule, caches):

@@ -30,6 +30,16 @@ joins the residual stream::
 Both sums happen in float32 inside the norm kernel that computes the output norm; the
 output norm of the mixer and the input norm of the feed-forward are one launch.  The
 block leaves nothing pending (it returns ``None``).
+
+``hyper`` is a pre-norm block over several residual streams (hyper-connections): each of its
+norms (:class:`~.norm.HyperNorm`) forms its sublayer's input from all streams and owns the weights
+by which the sublayer's output joins them; the output travels on as a pending branch that the
+next such norm folds in::
+
+    h = norm1(pending, streams)            # the pending branch joins the streams; u = sum_s in1[s] x_s
+    pending = (mixer(h), mix1, out1)
+    h = norm2(pending, streams)
+    return (feed_forward(h), mix2, out2)   # the next layer's first norm (or the last norm) adds it
 """
 
 from __future__ import annotations
@@ -105,3 +115,26 @@ class SandwichBlock(Block):
         f = self.feed_forward.forward(ctx, h)
         self.norms["feed_forward_out"].add_normed(ctx, f, residual, self.mult)
         return None
+
+
+@register_block("hyper")
+class HyperBlock(Block):
+    NORM_NAMES = ("mixer", "feed_forward")
+    HAS_FEED_FORWARD = True          # or none: then only the mixer's norm
+
+    @classmethod
+    def check_parts(cls, prefix, norm_names, has_feed_forward) -> None:
+        want = cls.NORM_NAMES if has_feed_forward else cls.NORM_NAMES[:1]
+        if sorted(norm_names) != sorted(want):
+            raise ValueError(f"layer '{prefix}': a hyper block {'with' if has_feed_forward else 'without'} "
+                             f"feed-forward has the norms {list(want)}, the layer lists {sorted(norm_names)}")
+
+    def forward(self, ctx, delta, residual, cache):
+        first = self.norms["mixer"]
+        h = first.forward(ctx, delta, residual)
+        pending = first.pending(self.mixer.forward(ctx, h, cache))
+        if self.feed_forward is None:
+            return pending
+        second = self.norms["feed_forward"]
+        h = second.forward(ctx, pending, residual)
+        return second.pending(self.feed_forward.forward(ctx, h))

@@ -23,7 +23,9 @@ from .base import FeedForward, StepContext, register_feed_forward
 class DenseMLP(FeedForward):
     """params: ``hidden_size, intermediate_size, activation``, ``scope`` and ``names``
     (up, down below the scope); ``gated`` (default False): a gate projection beside the up
-    projection (``names`` then also has gate, and gate_up for the merged matrix the model keeps)."""
+    projection (``names`` then also has gate, and gate_up for the merged matrix the model keeps).
+    A gated feed-forward may also take the clamped pair ``swigluoai`` with ``act_alpha`` and
+    ``act_limit``: ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``, ``g sigmoid(alpha g) (u + 1)``."""
 
     graph_capturable = True
     writes_into_out = True
@@ -34,8 +36,11 @@ class DenseMLP(FeedForward):
         self.hidden = int(p["hidden_size"])
         self.inter = int(p["intermediate_size"])
         self.act = str(p.get("activation", "relu2"))
-        if self.act not in ops.ACTIVATIONS:
-            raise ValueError(f"activation {self.act!r} is not one of {sorted(ops.ACTIVATIONS)}")
+        self.act_alpha = float(p.get("act_alpha", 1.702))
+        self.act_limit = float(p.get("act_limit", 7.0))
+        known = ops.GLU_KINDS if p.get("gated", False) else ops.ACTIVATIONS
+        if self.act not in known:
+            raise ValueError(f"activation {self.act!r} is not one of {sorted(known)}")
         scope = self.name(p["scope"])
         self.n_up = f"{scope}.{p['names']['up']}"
         self.n_down = f"{scope}.{p['names']['down']}"
@@ -67,7 +72,7 @@ class DenseMLP(FeedForward):
             # one product against [gate; up], then f(gate) * up in float32
             both = linear.linear(x, self.w_up, ws.get("mlp.gate_up", (T, 2 * self.inter), ctx.dtype))
             mid = ws.get("mlp.mid", (T, self.inter), ctx.dtype)
-            ops.glu_rows(both, mid, self.act)
+            ops.glu_rows(both, mid, self.act, self.act_alpha, self.act_limit)
             if out is None:
                 out = ws.get("mlp.y", (T, self.hidden), ctx.dtype)
             return linear.linear(mid, self.w_down, out)

@@ -62,7 +62,10 @@ class RoutedExperts(FeedForward):
     (sigmoid | softmax), ``use_bias, renormalize, scale, activation`` (silu |
     swigluoai), ``act_alpha, act_limit, scope`` and ``checkpoint_names``
     (router, bias, gate_up, down: model-side names below the scope; gate, up,
-    down_each: per-expert checkpoint names with ``{e}``)."""
+    down_each: per-expert checkpoint names with ``{e}``).  ``groups`` and ``keep_groups``
+    (default 1, 1: no groups): the experts form ``groups`` equal groups of neighbours, a group's
+    value is the sum of its two largest choice scores (score plus bias), and only experts of the
+    ``keep_groups`` best groups can be chosen."""
 
     graph_capturable = True
 
@@ -82,6 +85,12 @@ class RoutedExperts(FeedForward):
         self.act_limit = float(p.get("act_limit", 7.0))
         if self.k > self.E:
             raise ValueError(f"top_k {self.k} exceeds num_experts {self.E}")
+        self.groups = int(p.get("groups", 1))
+        self.keep_groups = int(p.get("keep_groups", self.groups))
+        if (self.groups < 1 or self.E % self.groups or not 1 <= self.keep_groups <= self.groups
+                or self.keep_groups * (self.E // self.groups) < self.k or self.groups > 256):
+            raise ValueError(f"{self.groups} groups of which {self.keep_groups} are kept do not fit "
+                             f"{self.E} experts, top-{self.k}")
         names = p["checkpoint_names"]
         self.scope = self.name(p["scope"])
         self.n_router = f"{self.scope}.{names['router']}"
@@ -145,10 +154,10 @@ class RoutedExperts(FeedForward):
         weights = ws.get("moe.weights", (T, self.k), torch.float32)
         if sort_into is not None and ops.route_small_takes(T, self.E, self.k):
             ops.route_small(logits, self.w_bias, ids, weights, *sort_into, self.k, self.softmax,
-                            self.renorm, self.scale, terms)
+                            self.renorm, self.scale, terms, self.groups, self.keep_groups)
             return ids, weights, True
         ops.router_select(logits, self.w_bias, ids, weights, self.k, self.softmax, self.renorm,
-                          self.scale, terms)
+                          self.scale, terms, self.groups, self.keep_groups)
         return (ids, weights) if sort_into is None else (ids, weights, False)
 
     def forward(self, ctx: StepContext, x: torch.Tensor) -> torch.Tensor:

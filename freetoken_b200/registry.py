@@ -27,6 +27,10 @@ class Architecture:
     build_plan: Callable[[Any], ModelPlan]
     config_to_dict: Callable[[Any], Dict[str, Any]]
     rename_tensor: Callable[[str], Optional[str]] = lambda name: name
+    # ``(config.json dict, {checkpoint tensor name: shape}) -> dict`` for a design some of whose sizes
+    # only the checkpoint's tensor shapes state; called with the file headers of a model folder
+    # before ``read_config``
+    sizes_from_tensors: Optional[Callable[[Mapping[str, Any], Mapping[str, Tuple[int, ...]]], Mapping[str, Any]]] = None
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
@@ -69,6 +73,15 @@ def read_model_config(folder_or_file: str) -> Tuple[Architecture, Any]:
     with open(path) as f:
         raw = json.load(f)
     arch = architecture_of(raw)
+    if arch.sizes_from_tensors is not None and os.path.isdir(folder_or_file):
+        from .weights.safetensors_io import Checkpoint
+        with Checkpoint(folder_or_file) as ckpt:
+            shapes = {}
+            for name, entry in ckpt.entries.items():
+                model_name = arch.rename_tensor(name)
+                if model_name is not None:
+                    shapes[model_name] = tuple(entry.shape)
+        raw = arch.sizes_from_tensors(raw, shapes)
     return arch, arch.read_config(raw)
 
 
@@ -98,6 +111,16 @@ def _load_builtin() -> None:
             read_config=fazinex.FazinexConfig.from_dict,
             build_plan=fazinex.build_plan,
             config_to_dict=lambda cfg: cfg.to_dict(),
+        ),
+    )
+    from .config import nirelix
+    register_architecture(
+        Architecture(
+            name=nirelix.ARCHITECTURE,
+            read_config=nirelix.NirelixConfig.from_dict,
+            build_plan=nirelix.build_plan,
+            config_to_dict=lambda cfg: cfg.to_dict(),
+            sizes_from_tensors=nirelix.sizes_from_tensors,
         ),
     )
     from .config import tonapel

@@ -88,6 +88,8 @@ def random_tensor(spec: TensorSpec, seed: int, device, dtype: torch.dtype,
             continue
         draw = torch.randn(end - begin, generator=gen, device=device, dtype=torch.float32)
         flat[begin:end] = (draw * std + spec.init.mean).to(dtype)
+    if spec.init.eye and out.dim() == 2 and out.shape[0] == out.shape[1]:
+        out += torch.eye(out.shape[0], dtype=torch.float32, device=device).mul_(spec.init.eye).to(dtype)
     return out
 
 

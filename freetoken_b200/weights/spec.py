@@ -99,10 +99,12 @@ def take_apart(src: Source, tensor: torch.Tensor, out: dict) -> None:
 
 @dataclass(frozen=True)
 class Init:
-    """How the random-weights mode fills a tensor: ``mean + std * N(0,1)``."""
+    """How the random-weights mode fills a tensor: ``mean + std * N(0,1)``, plus ``eye`` on the
+    diagonal of a square matrix."""
 
     mean: float = 0.0
     std: float = 0.02
+    eye: float = 0.0
 
 
 @dataclass(frozen=True)
