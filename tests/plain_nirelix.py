@@ -155,8 +155,10 @@ def dense_ff(h, w, p, mlp):
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ w[p + "down"].T
 
 
-def choose_experts(h, w, p, router):
-    """``(ids [T, top], weights [T, top])``: the largest choice scores inside the best groups."""
+def choose_experts(h, w, p, router, margins=None):
+    """``(ids [T, top], weights [T, top])``: the largest choice scores inside the best groups.
+    ``margins`` (a list) receives, per token, by how much the last chosen expert beat the first one
+    left out, and the last kept group the first one dropped."""
     E, top = router["experts"], router["top"]
     groups = router.get("groups") or {"count": 1, "keep": 1}
     s = torch.sigmoid(h @ w[p + "router"].T)
@@ -167,15 +169,25 @@ def choose_experts(h, w, p, router):
     kept = group_score.topk(groups["keep"], dim=-1).indices
     allowed = torch.zeros_like(group_score, dtype=torch.bool).scatter_(1, kept, True)
     allowed = allowed[:, :, None].expand(-1, -1, per).reshape(-1, E)
-    ids = choice.masked_fill(~allowed, float("-inf")).topk(top, dim=-1).indices
+    masked = choice.masked_fill(~allowed, float("-inf"))
+    ids = masked.topk(top, dim=-1).indices
+    if margins is not None:
+        m = torch.full((h.shape[0],), float("inf"), dtype=h.dtype)
+        if top < E:
+            best = masked.topk(top + 1, dim=-1).values
+            m = torch.minimum(m, best[:, top - 1] - best[:, top])
+        if groups["keep"] < groups["count"]:
+            best = group_score.topk(groups["keep"] + 1, dim=-1).values
+            m = torch.minimum(m, best[:, -2] - best[:, -1])
+        margins.append(m)
     picked = s.gather(1, ids)
     return ids, picked / (picked.sum(-1, keepdim=True) + 1e-20) * router["scale"]
 
 
-def expert_ff(h, w, p, mlp, ids=None):
+def expert_ff(h, w, p, mlp, ids=None, margins=None):
     """``ids`` (``[T, top]``) overrides the choice; the weights are always those of the scores."""
     router = mlp["router"]
-    own_ids, weights = choose_experts(h, w, p, router)
+    own_ids, weights = choose_experts(h, w, p, router, margins)
     if ids is not None:
         s = torch.sigmoid(h @ w[p + "router"].T).gather(1, ids)
         weights = s / (s.sum(-1, keepdim=True) + 1e-20) * router["scale"]
@@ -199,10 +211,10 @@ def sublayer(streams, w, prefix, q, fn, eps):
     return torch.einsum("sr,stw->rtw", w[hc + "mix"], streams) + w[hc + "out"][:, None, None] * y[None]
 
 
-def forward(cfg, w, tokens, expert_ids=None, trace=None):
+def forward(cfg, w, tokens, expert_ids=None, trace=None, margins=None):
     """Logits ``[T, vocab]`` of one sequence.  ``expert_ids``: ``{layer: ids [T, top]}`` to use
     instead of the plain choice; ``trace``: a list that receives the sum of the streams after
-    every layer."""
+    every layer; ``margins``: a list that receives every routed layer's choice margins."""
     eps = cfg["norm"]["eps"]
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     streams = x[None].repeat(cfg.get("streams", 1), 1, 1)
@@ -215,7 +227,7 @@ def forward(cfg, w, tokens, expert_ids=None, trace=None):
             if mlp.get("kind", "dense") == "dense":
                 ff = lambda h: dense_ff(h, w, p + "mlp.", mlp)
             else:
-                ff = lambda h: expert_ff(h, w, p + "mlp.", mlp, None if expert_ids is None else expert_ids.get(i))
+                ff = lambda h: expert_ff(h, w, p + "mlp.", mlp, None if expert_ids is None else expert_ids.get(i), margins)
             streams = sublayer(streams, w, p, 2, ff, eps)
         if trace is not None:
             trace.append(streams.sum(0))
@@ -240,6 +252,8 @@ def expected_tensors(cfg):
                         x + "o": (W, H * V)})
         elif layer["type"] == "channel_delta":
             H, G, D, V, taps, low = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"], m["low_rank"]
+            # (low_rank: the one size a checkpoint states only through its tensor shapes; the tests'
+            # configurations carry it so that weights can be made, the files' config.json does not)
             out.update({x + "q": (G * D, W), x + "k": (G * D, W), x + "v": (H * V, W),
                         x + "q.conv": (G * D, taps), x + "k.conv": (G * D, taps), x + "v.conv": (H * V, taps),
                         x + "b": (H, W), x + "A_log": (H,), x + "norm": (V,), x + "a1": (low, W),
