@@ -132,6 +132,8 @@ class HyperNorm(Norm):
         return PendingBranch(y, self.w_mix, self.w_out)
 
     def forward(self, ctx: StepContext, delta, residual: torch.Tensor) -> torch.Tensor:
+        if residual.dim() == 2 and self.streams == 1:
+            residual = residual.unsqueeze(1)          # one stream: the plain residual [T, H]
         if residual.dim() != 3 or residual.shape[1] != self.streams:
             raise ValueError(f"hyper_norm: the residual must be [T, {self.streams}, H]")
         if delta is not None and not isinstance(delta, PendingBranch):

@@ -238,7 +238,7 @@ def test_retention_scan_in_segments(dtype, H, D, P, rot):
         g = torch.cat(got[r]).double()
         scale = float(want[r].abs().max())
         assert float((g - want[r]).abs().max()) < (3e-5 if dtype == "float32" else 2e-2) * scale, r
-    assert float(state[1].abs().max()) == 0 and bool((state[:, H * D * P:] == 7.0).all())
+    assert float(state[1, :H * D * P].abs().max()) == 0 and bool((state[:, H * D * P:] == 7.0).all())
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
@@ -430,7 +430,7 @@ def only_the_target_writes(config, state, target, kind):
         state["l0.mix.b"] = row.repeat(heads, 1).to(torch.bfloat16).double()
     else:
         v = state["l0.mix.v"]
-        y = 0.02 * (h @ v.T)                                   # everybody's values shrink ...
+        y = 0.05 * (h @ v.T)                                   # everybody's values shrink ...
         y[target] = 3.0 * (h[target] @ v.T)                    # ... but the target's grow
         state["l0.mix.v"] = torch.linalg.lstsq(h, y).solution.T.contiguous().to(torch.bfloat16).double()
 
@@ -446,14 +446,15 @@ def test_a_far_token_reaches_through_the_state(tmp_path, kind, dtype):
         layer = nx.retention(3, 24, 12, (0.999, 0.9995, 1.0), 16)
     else:
         layer = nx.channel_delta(3, 1, 24, 12, 3, 6)
-    config = nx.one_layer(layer, vocab=40, width=48, streams=2)
+    vocab = 24 if kind == "retention" else 40
+    config = nx.one_layer(layer, vocab=vocab, width=48, streams=2)
     state = nx.random_state(config, 51, slow_decay=True)
     target, stand_in = 5, 6
     only_the_target_writes(config, state, target, kind)
     page, n = 16, 300
     reqs = {}
     for place in (15, 16, 17, 0, 49):
-        toks = [t if t != target else stand_in for t in nx.tokens(70 + place, n, 40)]
+        toks = [t if t != target else stand_in for t in nx.tokens(70 + place, n, vocab)]
         toks[place] = target
         reqs[f"t{place}"] = toks
     want = {rid: plain.forward(config, state, t) for rid, t in reqs.items()}
@@ -461,10 +462,13 @@ def test_a_far_token_reaches_through_the_state(tmp_path, kind, dtype):
     other[16] = stand_in
     assert float(nx.position_errors(plain.forward(config, state, other)[-1:], want["t16"][-1:])) > 0.3
     folder = nx.write(str(tmp_path / "m"), config, state)
+    # retention in bfloat16: the shrunk values are small differences of large products of a rounded input
+    # (4 % off by construction, whatever computes them); the effect looked for is ten times that
+    tol = nx.TOL[dtype] * (2 if (kind, dtype) == ("retention", "bfloat16") else 1)
     for cut in ("decode_tail", "portions", "mixed"):
         schedule = CUTS[cut](reqs)
         engine = nx.make_engine(folder, dtype, page, rd.peak_tokens(schedule, page), poison=True)
-        nx.compare(run_engine(engine, reqs, schedule), want, nx.TOL[dtype], f"far token, {kind}, {cut} [{dtype}]")
+        nx.compare(run_engine(engine, reqs, schedule), want, tol, f"far token, {kind}, {cut} [{dtype}]")
 
 
 # --------------------------------------------------------- first tokens, long decoding
