@@ -235,7 +235,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--equivalence", action="store_true",
                    help="instead of timing: the same random model (--layers, default 2) in float32 and in "
                         "bfloat16 on one 512-token prompt and 8 decoded tokens; prints how far the logits differ")
-    p.add_argument("--design", default=None, choices=["fazinex", "tonapel"],
+    p.add_argument("--design", default=None, choices=["fazinex", "tonapel", "nirelix"],
                    help="instead of the default workload: this design beside the MiniMax-M3 decoder at "
                         "equal size (prefill and decode steps, and the design's kernels against their rooflines)")
     p.add_argument("--sizes", default="w2048,w4096", help="with --design: which layer sizes to run")
@@ -262,6 +262,9 @@ def main(argv: Optional[List[str]] = None) -> int:
         from . import design_bench, tonapel_bench
         if a.steps == 256:
             a.steps = 64
+        if a.design == "nirelix":
+            from . import nirelix_bench
+            return nirelix_bench.main(a)
         return (tonapel_bench if a.design == "tonapel" else design_bench).main(a)
 
     from .csrc import ops

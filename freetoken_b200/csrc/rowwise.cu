@@ -494,6 +494,118 @@ hyper_norm_kernel(float* __restrict__ streams, const AT* __restrict__ branch, in
     dst[c] = from_float<AT>((u_row[c] - mean) * inv * weight[c] + (bias ? bias[c] : 0.f));
 }
 
+// The same launch for rows of a multiple of 4 values with 16-byte aligned rows, S known at compile time:
+// a thread owns up to KEEP groups of 4 consecutive values; it first fetches all its pieces of every
+// stream and of the branch (all loads in flight together), then joins, reads and keeps u in registers
+// between the passes.  The sums run in the order of the generic kernel.
+template <typename AT, int S, int KEEP>
+__global__ void __launch_bounds__(256)
+hyper_norm_vec_kernel(float* __restrict__ streams, const AT* __restrict__ branch, int k, const float* __restrict__ mix,
+                      const float* __restrict__ out_w, const float* __restrict__ read,
+                      const float* __restrict__ weight, const float* __restrict__ bias, float eps, int center,
+                      AT* __restrict__ normed, int H) {
+  __shared__ float scratch[33];
+  pdl_wait();
+  const int t = blockIdx.x, groups = H >> 2;
+  float m[S * S], ow[S], rd[S];
+#pragma unroll
+  for (int i = 0; i < S * S; ++i) m[i] = branch ? mix[i] : 0.f;
+#pragma unroll
+  for (int i = 0; i < S; ++i) {
+    ow[i] = branch ? out_w[i] : 0.f;
+    rd[i] = read ? read[i] : 1.f;
+  }
+  float* x = streams + (size_t)t * S * H;
+  const AT* y_rows = branch ? branch + (size_t)t * k * H : nullptr;
+  float4 xs[KEEP][S], y[KEEP];
+#pragma unroll
+  for (int j = 0; j < KEEP; ++j) {
+    const int gi = threadIdx.x + j * 256;
+    y[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (gi < groups) {
+#pragma unroll
+      for (int s_ = 0; s_ < S; ++s_) xs[j][s_] = load4f(x + (size_t)s_ * H + 4 * gi);
+      if (branch) {
+        for (int q = 0; q < k; ++q) {
+          const float4 v = load4f(y_rows + (size_t)q * H + 4 * gi);
+          y[j].x += v.x; y[j].y += v.y; y[j].z += v.z; y[j].w += v.w;
+        }
+      }
+    }
+  }
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < KEEP; ++j) {
+    const int gi = threadIdx.x + j * 256;
+    if (gi < groups) {
+      float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (branch) {
+#pragma unroll
+        for (int r = 0; r < S; ++r) {
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int s_ = 0; s_ < S; ++s_) {
+            const float c = m[s_ * S + r];
+            v.x = fmaf(c, xs[j][s_].x, v.x); v.y = fmaf(c, xs[j][s_].y, v.y);
+            v.z = fmaf(c, xs[j][s_].z, v.z); v.w = fmaf(c, xs[j][s_].w, v.w);
+          }
+          v.x = fmaf(ow[r], y[j].x, v.x); v.y = fmaf(ow[r], y[j].y, v.y);
+          v.z = fmaf(ow[r], y[j].z, v.z); v.w = fmaf(ow[r], y[j].w, v.w);
+          store4f(x + (size_t)r * H + 4 * gi, v);
+          u.x = fmaf(rd[r], v.x, u.x); u.y = fmaf(rd[r], v.y, u.y); u.z = fmaf(rd[r], v.z, u.z); u.w = fmaf(rd[r], v.w, u.w);
+        }
+      } else {
+#pragma unroll
+        for (int s_ = 0; s_ < S; ++s_) {
+          u.x = fmaf(rd[s_], xs[j][s_].x, u.x); u.y = fmaf(rd[s_], xs[j][s_].y, u.y);
+          u.z = fmaf(rd[s_], xs[j][s_].z, u.z); u.w = fmaf(rd[s_], xs[j][s_].w, u.w);
+        }
+      }
+      y[j] = u;
+      sum += u.x; sum += u.y; sum += u.z; sum += u.w;
+    }
+  }
+  if (!normed) return;
+  float mean = 0.f;
+  if (center) mean = block_sum(sum, scratch) / (float)H;
+  float sq = 0.f;
+#pragma unroll
+  for (int j = 0; j < KEEP; ++j) {
+    if ((int)threadIdx.x + j * 256 < groups) {
+      float4& u = y[j];
+      u.x -= mean; u.y -= mean; u.z -= mean; u.w -= mean;
+      sq = fmaf(u.x, u.x, sq); sq = fmaf(u.y, u.y, sq); sq = fmaf(u.z, u.z, sq); sq = fmaf(u.w, u.w, sq);
+    }
+  }
+  const float inv = 1.f / sqrtf(block_sum(sq, scratch) / (float)H + eps);
+  AT* dst = normed + (size_t)t * H;
+#pragma unroll
+  for (int j = 0; j < KEEP; ++j) {
+    const int gi = threadIdx.x + j * 256;
+    if (gi < groups) {
+      const float4 w = load4f(weight + 4 * gi);
+      const float4 b = bias ? load4f(bias + 4 * gi) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 u = y[j];
+      store4f(dst + 4 * gi, make_float4(u.x * inv * w.x + b.x, u.y * inv * w.y + b.y, u.z * inv * w.z + b.z,
+                                        u.w * inv * w.w + b.w));
+    }
+  }
+}
+
+template <typename AT, int S>
+static cudaError_t launch_hyper_vec(cudaStream_t stream, int T, int H, float* streams, const AT* branch, int k,
+                                    const float* mix, const float* out_w, const float* read, const float* weight,
+                                    const float* bias, float eps, int center, AT* normed) {
+  if (H <= 2048)
+    return launch_pdl(hyper_norm_vec_kernel<AT, S, 2>, dim3(T), dim3(256), 0, stream, streams, branch, k, mix, out_w,
+                      read, weight, bias, eps, center, normed, H);
+  if (H <= 4096)
+    return launch_pdl(hyper_norm_vec_kernel<AT, S, 4>, dim3(T), dim3(256), 0, stream, streams, branch, k, mix, out_w,
+                      read, weight, bias, eps, center, normed, H);
+  return launch_pdl(hyper_norm_vec_kernel<AT, S, 8>, dim3(T), dim3(256), 0, stream, streams, branch, k, mix, out_w, read,
+                    weight, bias, eps, center, normed, H);
+}
+
 // Rows of a column range of a wider matrix, RMS-normed and multiplied by a weight:
 // out[t, :] = x[t, :] / sqrt(mean(x[t, :]^2) + eps) * w.   One block per row.
 template <typename AT>
@@ -724,6 +836,25 @@ int ft_hyper_norm(float* streams, const void* branch, int k, const float* mix, c
                   int T, int S, int H, int dtype, cudaStream_t stream) {
   if (T <= 0) return FT_OK;
   if (S < 1 || S > HYPER_MAX_STREAMS || H <= 0 || H > 10240 || (branch && k <= 0)) return FT_ERR_SHAPE;
+  const bool vec = !(H & 3) && H <= 8192 && S <= 4 && !((uintptr_t)streams & 15) && !((uintptr_t)branch & 15) &&
+                   !((uintptr_t)weight & 15) && !((uintptr_t)bias & 15) && !((uintptr_t)normed & 15) &&
+                   (dtype == FT_DTYPE_F32 || !(H & 7));
+  if (vec) {
+    cudaError_t e = cudaSuccess;
+    FT_DISPATCH(dtype, AT, {
+      const AT* b = (const AT*)branch;
+      AT* o = (AT*)normed;
+      switch (S) {
+        case 1: e = launch_hyper_vec<AT, 1>(stream, T, H, streams, b, k, mix, out_w, read, weight, bias, eps, center, o); break;
+        case 2: e = launch_hyper_vec<AT, 2>(stream, T, H, streams, b, k, mix, out_w, read, weight, bias, eps, center, o); break;
+        case 3: e = launch_hyper_vec<AT, 3>(stream, T, H, streams, b, k, mix, out_w, read, weight, bias, eps, center, o); break;
+        default: e = launch_hyper_vec<AT, 4>(stream, T, H, streams, b, k, mix, out_w, read, weight, bias, eps, center, o); break;
+      }
+    });
+    if (e != cudaSuccess) return (int)e;
+    FT_LAUNCH_CHECK();
+    return FT_OK;
+  }
   FT_DISPATCH(dtype, AT,
               (launch_pdl(hyper_norm_kernel<AT>, dim3(T), dim3(256), (size_t)H * sizeof(float), stream, streams,
                           (const AT*)branch, k, mix, out_w, read, weight, bias, eps, center, (AT*)normed, S, H)));
