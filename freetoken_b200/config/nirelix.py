@@ -15,7 +15,8 @@ A layer is a mixer sublayer and, unless its ``mlp`` is null, a feed-forward subl
   channel, ``exp(-exp(A_h) softplus(W_a2 W_a1 h + dt_bias))``, a read-out norm whose weight the heads
   share, and a gate ``sigmoid(W_g2 W_g1 h)``.  The width of the middle of the two-step projections
   is the one size config.json does not state: it is read from the checkpoint's tensor shapes
-  (:func:`sizes_from_tensors`), or given as ``mixer.low_rank`` for a model without a checkpoint;
+  (:func:`sizes_from_tensors`), or given as ``mixer.low_rank`` (and ``mixer.gate_rank`` where the gate's
+  middle has another width than the decay's) for a model without a checkpoint;
 * ``latent_attention``: queries through a normed latent, keys and values made from a normed latent
   of ``kv_rank`` values plus ``rot_dim`` rotated key values shared by the heads (pairs ``(2i, 2i + 1)``),
   softmax inside a sliding window, a sigmoid gate per output value.
@@ -70,6 +71,7 @@ class ChannelDeltaMixer:
     vdim: int
     conv: int
     low_rank: int
+    gate_rank: int
 
 
 @dataclass(frozen=True)
@@ -142,7 +144,8 @@ def _read_retention(m: Any, where: str) -> RetentionMixer:
 def _read_channel_delta(m: Any, where: str) -> ChannelDeltaMixer:
     d = ChannelDeltaMixer(heads=int(_need(m, "heads", where)), kv_heads=int(m.get("kv_heads") or m["heads"]),
                           dim=int(_need(m, "dim", where)), vdim=int(m.get("vdim") or m["dim"]),
-                          conv=int(_need(m, "conv", where)), low_rank=int(m.get("low_rank") or 0))
+                          conv=int(_need(m, "conv", where)), low_rank=int(m.get("low_rank") or 0),
+                          gate_rank=int(m.get("gate_rank") or m.get("low_rank") or 0))
     _positive(where, heads=d.heads, kv_heads=d.kv_heads, dim=d.dim, vdim=d.vdim, conv=d.conv)
     if d.heads % d.kv_heads:
         raise ConfigError(f"config.json: '{where}kv_heads' = {d.kv_heads} does not divide heads = {d.heads}")
@@ -241,15 +244,17 @@ class NirelixConfig:
 
 
 def sizes_from_tensors(raw: Mapping[str, Any], shapes: Mapping[str, Tuple[int, ...]]) -> Dict[str, Any]:
-    """``raw`` with the sizes that only the checkpoint states filled in: the width of the middle of a
-    ``channel_delta`` mixer's two-step projections is the number of rows of ``l<i>.mix.a1``."""
+    """``raw`` with the sizes that only the checkpoint states filled in: the widths of the middles of a
+    ``channel_delta`` mixer's two-step projections are the numbers of rows of ``l<i>.mix.a1`` (decay)
+    and ``l<i>.mix.g1`` (gate)."""
     out = dict(raw)
     layers = []
     for i, entry in enumerate(raw.get("layers") or []):
         if isinstance(entry, Mapping) and entry.get("type") == "channel_delta" and isinstance(entry.get("mixer"), Mapping):
-            shape = shapes.get(f"l{i}.mix.a1")
-            if shape and not entry["mixer"].get("low_rank"):
-                entry = {**entry, "mixer": {**entry["mixer"], "low_rank": int(shape[0])}}
+            for key, tensor in (("low_rank", "a1"), ("gate_rank", "g1")):
+                shape = shapes.get(f"l{i}.mix.{tensor}")
+                if shape and not entry["mixer"].get(key):
+                    entry = {**entry, "mixer": {**entry["mixer"], key: int(shape[0])}}
         layers.append(entry)
     out["layers"] = layers
     return out
@@ -267,7 +272,7 @@ def _mixer_spec(cfg: NirelixConfig, layer: NirelixLayer) -> PartSpec:
     if layer.type == "channel_delta":
         return PartSpec("channel_delta", {
             "hidden_size": W, "heads": m.heads, "key_heads": m.kv_heads, "key_dim": m.dim, "head_dim": m.vdim,
-            "conv_taps": m.conv, "low_rank": m.low_rank, "norm_eps": cfg.norm_eps, "unit_eps": UNIT_NORM_EPS,
+            "conv_taps": m.conv, "low_rank": m.low_rank, "gate_rank": m.gate_rank, "norm_eps": cfg.norm_eps, "unit_eps": UNIT_NORM_EPS,
             "scope": "mix",
             "names": {"q": "q", "k": "k", "v": "v", "beta": "b", "decay_down": "a1", "decay_up": "a2",
                       "gate_down": "g1", "gate_up": "g2", "q_conv": "q.conv", "k_conv": "k.conv",

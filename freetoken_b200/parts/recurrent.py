@@ -197,7 +197,8 @@ class GatedDelta(_Recurrent):
 @register_mixer("channel_delta")
 class ChannelDelta(_Recurrent):
     """params: ``hidden_size, heads, key_heads, key_dim, head_dim, conv_taps, low_rank`` (the width of
-    the middle of the decay's and the gate's two-step projections), ``norm_eps, unit_eps``, ``scope``
+    the middle of the decay's two-step projection), ``gate_rank`` (the same of the gate's; default:
+    ``low_rank``), ``norm_eps, unit_eps``, ``scope``
     and ``names`` (q, k, v, beta: projections; decay_down, decay_up, gate_down, gate_up: the two steps
     of the decay's and the gate's; q_conv, k_conv, v_conv; a_log, dt_bias, norm, o; in and conv: the
     merged projection and convolution the model keeps).  ``dt_bias`` has one entry per head and key
@@ -213,9 +214,10 @@ class ChannelDelta(_Recurrent):
         self.P = int(p["head_dim"])
         self.taps = int(p["conv_taps"])
         self.low = int(p["low_rank"])
+        self.gate_low = int(p.get("gate_rank") or self.low)
         self.eps = float(p["norm_eps"])
         self.unit_eps = float(p.get("unit_eps", 1e-6))
-        if self.heads % self.G or self.taps < 1 or self.D > 256 or self.low < 1:
+        if self.heads % self.G or self.taps < 1 or self.D > 256 or self.low < 1 or self.gate_low < 1:
             raise ValueError("channel_delta: heads must be a multiple of key_heads, key_dim at most 256")
         self.inner = self.heads * self.P
         self.conv_channels = 2 * self.G * self.D + self.inner
@@ -228,7 +230,7 @@ class ChannelDelta(_Recurrent):
         n, H = self.names, self.hidden
         kd = self.G * self.D
         small = dict(role="small32", tag="recurrent")
-        rows = (("q", kd), ("k", kd), ("v", self.inner), ("decay_down", self.low), ("gate_down", self.low),
+        rows = (("q", kd), ("k", kd), ("v", self.inner), ("decay_down", self.low), ("gate_down", self.gate_low),
                 ("beta", self.heads))
         convs = (("q_conv", kd), ("k_conv", kd), ("v_conv", self.inner))
         return [
@@ -237,7 +239,7 @@ class ChannelDelta(_Recurrent):
             TensorSpec(n["conv"], (self.conv_channels, self.taps), init=Init(0.0, 0.3),
                        sources=(Cat(tuple(Name(n[key], (r, self.taps)) for key, r in convs), 0),), **small),
             TensorSpec(n["decay_up"], (self.heads * self.D, self.low), init=Init(0.0, 0.2)),
-            TensorSpec(n["gate_up"], (self.inner, self.low), init=Init(0.0, 0.2)),
+            TensorSpec(n["gate_up"], (self.inner, self.gate_low), init=Init(0.0, 0.2)),
             TensorSpec(n["a_log"], (self.heads,), init=Init(-1.0, 0.5), **small),
             TensorSpec(n["dt_bias"], (self.heads * self.D,), init=Init(-1.0, 0.5), **small),
             TensorSpec(n["norm"], (self.P,), role="small32", init=Init(1.0, 0.0), tag="norm"),
@@ -251,17 +253,18 @@ class ChannelDelta(_Recurrent):
     def forward(self, ctx: StepContext, x: torch.Tensor, cache: CacheView, out=None) -> torch.Tensor:
         T, ws, w = x.shape[0], ctx.workspace, self.w
         C, inner, heads, low = self.conv_channels, self.inner, self.heads, self.low
+        both = low + self.gate_low
         conv_state, state = self._states(cache)
-        proj = linear.linear(x, w["in"], ws.get("cdelta.in", (T, C + 2 * low + heads), ctx.dtype))
+        proj = linear.linear(x, w["in"], ws.get("cdelta.in", (T, C + both + heads), ctx.dtype))
         qkv = ws.get("cdelta.qkv", (T, C), ctx.dtype)
         ops.conv_silu(proj[:, :C], qkv, w["conv"], None, conv_state, ctx.token_seg, ctx.seg_slot,
                       ctx.seg_q_start)
         # the decay's second step leaves its float32 accumulator: softplus and exp follow in float32
         decay = linear.linear(proj[:, C:C + low], w["decay_up"], ws.get("cdelta.decay", (T, heads * self.D),
                                                                         torch.float32))
-        gate = linear.linear(proj[:, C + low:C + 2 * low], w["gate_up"], ws.get("cdelta.gate", (T, inner), ctx.dtype))
+        gate = linear.linear(proj[:, C + low:C + both], w["gate_up"], ws.get("cdelta.gate", (T, inner), ctx.dtype))
         o = ws.get("cdelta.o", (T, inner), torch.float32)
-        ops.channel_delta_scan(qkv, proj[:, C + 2 * low:], decay, w["dt_bias"], w["a_log"], state, o, ctx.seg_slot,
+        ops.channel_delta_scan(qkv, proj[:, C + both:], decay, w["dt_bias"], w["a_log"], state, o, ctx.seg_slot,
                                ctx.seg_q_start, heads, self.G, self.D, self.P, self.unit_eps, self.D ** -0.5)
         gated = ws.get("cdelta.gated", (T, inner), ctx.dtype)
         ops.gated_norm(o, gate, w["norm"], gated, heads, self.eps, gate_first=False, gate_kind="sigmoid")

@@ -4,7 +4,7 @@ The configurations differ from each other in every size and constant: widths, st
 two, four), head counts, key sizes below, equal to and above value sizes, windows of 1, of a few
 tokens, shorter and longer than a page, rotation of a part of a head and of all of it, latents
 narrower and wider than the heads, groups of experts of one, two and four of which one, some or
-all are kept, convolutions of 1 to 4 taps, layers without feed-forward, every layer order.
+all are kept, convolutions of 1 to 4 taps, two-step projections whose middles are equal or not, layers without feed-forward, every layer order.
 """
 
 from __future__ import annotations
@@ -24,9 +24,11 @@ def retention(heads, dim, vdim, decay, rot_dims, base=10000.0, mlp=None):
                                            "rot": {"base": base, "dims": rot_dims}}, "mlp": mlp}
 
 
-def channel_delta(heads, kv_heads, dim, vdim, conv, low_rank, mlp=None):
-    return {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
-                                               "conv": conv, "low_rank": low_rank}, "mlp": mlp}
+def channel_delta(heads, kv_heads, dim, vdim, conv, low_rank, mlp=None, gate_rank=None):
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv, "low_rank": low_rank}
+    if gate_rank:
+        mixer["gate_rank"] = gate_rank
+    return {"type": "channel_delta", "mixer": mixer, "mlp": mlp}
 
 
 def latent(heads, dim, rot_dim, vdim, q_rank, kv_rank, window, base=10000.0, scale=None, mlp=None):
@@ -52,7 +54,7 @@ def model(vocab, width, streams, eps, layers):
 
 # awkward sizes, nothing a multiple of 8; a window of 7 and of 1; two streams; a layer without feed-forward
 NX_A: Dict = model(150, 40, 2, 1e-5, [
-    channel_delta(4, 2, 12, 10, 2, 5, moe(6, 2, 24, 3, 2, scale=1.5)),
+    channel_delta(4, 2, 12, 10, 2, 5, moe(6, 2, 24, 3, 2, scale=1.5), gate_rank=9),
     latent(3, 6, 4, 10, 14, 18, 7, base=100.0, mlp=dense(56, 0.8)),
     retention(3, 10, 6, (0.9, 0.97, 0.995), 6, base=300.0),
     latent(2, 12, 2, 5, 9, 20, 1, base=50.0, scale=0.4, mlp=moe(4, 3, 20, 1, 1)),
@@ -74,7 +76,7 @@ NX_B: Dict = model(320, 128, 4, 2e-6, [
 NX_C: Dict = model(97, 70, 1, 1e-4, [
     retention(1, 33, 9, (0.98,), 0, mlp=moe(1, 1, 30, 1, 1, scale=0.7)),
     channel_delta(6, 6, 8, 12, 1, 3, dense(100, 0.5)),
-    channel_delta(3, 1, 40, 36, 3, 24, moe(8, 4, 16, 2, 2)),
+    channel_delta(3, 1, 40, 36, 3, 24, moe(8, 4, 16, 2, 2), gate_rank=8),
     latent(6, 5, 8, 7, 11, 25, 33, base=1000.0),
 ])
 
@@ -127,6 +129,7 @@ def file_config(config: Dict) -> Dict:
     out = copy.deepcopy(config)
     for layer in out["layers"]:
         layer["mixer"].pop("low_rank", None)
+        layer["mixer"].pop("gate_rank", None)
     return out
 
 

@@ -252,13 +252,14 @@ def expected_tensors(cfg):
                         x + "o": (W, H * V)})
         elif layer["type"] == "channel_delta":
             H, G, D, V, taps, low = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"], m["low_rank"]
-            # (low_rank: the one size a checkpoint states only through its tensor shapes; the tests'
-            # configurations carry it so that weights can be made, the files' config.json does not)
+            glow = m.get("gate_rank") or low
+            # (low_rank, gate_rank: sizes a checkpoint states only through its tensor shapes; the tests'
+            # configurations carry them so that weights can be made, the files' config.json does not)
             out.update({x + "q": (G * D, W), x + "k": (G * D, W), x + "v": (H * V, W),
                         x + "q.conv": (G * D, taps), x + "k.conv": (G * D, taps), x + "v.conv": (H * V, taps),
                         x + "b": (H, W), x + "A_log": (H,), x + "norm": (V,), x + "a1": (low, W),
-                        x + "a2": (H * D, low), x + "dt_bias": (H * D,), x + "g1": (low, W),
-                        x + "g2": (H * V, low), x + "o": (W, H * V)})
+                        x + "a2": (H * D, low), x + "dt_bias": (H * D,), x + "g1": (glow, W),
+                        x + "g2": (H * V, glow), x + "o": (W, H * V)})
         else:
             H, D, R, V = m["heads"], m["dim"], m["rot_dim"], m["vdim"]
             out.update({x + "dq": (m["q_rank"], W), x + "dq.norm": (m["q_rank"],),

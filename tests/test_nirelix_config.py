@@ -48,8 +48,10 @@ def test_plan_hands_every_constant_to_a_part(which):
             assert (p["position"].kind, p["position"].params["rotary_dim"], p["position"].params["theta"]) == \
                 ("rotary_neox", m["rot"]["dims"], m["rot"]["base"])
         elif layer["type"] == "channel_delta":
-            assert (p["heads"], p["key_heads"], p["key_dim"], p["head_dim"], p["conv_taps"], p["low_rank"]) == \
-                (m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"], m["low_rank"])
+            assert (p["heads"], p["key_heads"], p["key_dim"], p["head_dim"], p["conv_taps"], p["low_rank"],
+                    p["gate_rank"]) == \
+                (m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"], m["low_rank"],
+                 m.get("gate_rank") or m["low_rank"])
         else:
             assert (p["num_heads"], p["qk_dim"], p["rot_dim"], p["v_dim"], p["q_rank"], p["rank"], p["sm_scale"],
                     p["sliding_window"], p["gate_per"]) == \
@@ -108,17 +110,20 @@ def test_cache_needs_rows_of_latent_plus_rotated_part_and_states():
 
 
 def test_a_size_only_the_checkpoint_states(tmp_path):
-    """config.json does not give the width of the middle of the delta rule's two-step projections:
-    it is the row count of the first step's matrix in the checkpoint."""
+    """config.json does not give the widths of the middles of the delta rule's two-step projections:
+    they are the row counts of the first steps' matrices in the checkpoint (the gate's may differ
+    from the decay's)."""
     config = nx.NX_C
     folder = nx.write(str(tmp_path / "m"), config, nx.random_state(config, 3))
     on_disk = json.load(open(os.path.join(folder, "config.json")))
-    assert all("low_rank" not in layer["mixer"] for layer in on_disk["layers"])
+    assert all("low_rank" not in layer["mixer"] and "gate_rank" not in layer["mixer"] for layer in on_disk["layers"])
     arch, cfg = read_model_config(folder)
-    assert [l.mixer.low_rank for l in cfg.layers if l.type == "channel_delta"] == [3, 24]
+    assert [(l.mixer.low_rank, l.mixer.gate_rank) for l in cfg.layers if l.type == "channel_delta"] == [(3, 3), (24, 8)]
     with pytest.raises(ConfigError, match="low_rank"):
         NirelixConfig.from_dict(on_disk)
-    assert sizes_from_tensors(on_disk, {"l1.mix.a1": (3, 70), "l2.mix.a1": (24, 70)})["layers"][2]["mixer"]["low_rank"] == 24
+    sized = sizes_from_tensors(on_disk, {"l1.mix.a1": (3, 70), "l2.mix.a1": (24, 70), "l2.mix.g1": (8, 70)})
+    assert (sized["layers"][2]["mixer"]["low_rank"], sized["layers"][2]["mixer"]["gate_rank"]) == (24, 8)
+    assert "gate_rank" not in sized["layers"][1]["mixer"]
 
 
 def _broken(path, value):
