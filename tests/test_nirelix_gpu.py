@@ -349,6 +349,21 @@ def test_cut_matches_plain(models, which, dtype, cut):
     run_and_compare(models[which], nx.NX[which], state, reqs, CUTS[cut](reqs), dtype, nx.PAGE[which], f"{which} {cut}")
 
 
+@pytest.mark.parametrize("which", list(nx.NX))
+def test_float32_cuts_agree_bitwise(models, which):
+    """In float32 the logits at a position depend neither on the cut nor on the batch: every
+    token runs the same operations in the same order whatever else the step holds."""
+    reqs = requests_of(which)
+    results = {}
+    for cut, fn in CUTS.items():
+        schedule = fn(reqs)
+        engine = nx.make_engine(models[which], "float32", nx.PAGE[which], rd.peak_tokens(schedule, nx.PAGE[which]))
+        results[cut] = run_engine(engine, reqs, schedule)
+    for cut in ("decode_tail", "portions", "mixed"):
+        for rid in reqs:
+            assert torch.equal(results[cut][rid], results["whole"][rid]), (cut, rid)
+
+
 def test_fast_attention_kernels_take_the_latent_rows(models, monkeypatch):
     """Configuration B in bfloat16 (cached rows of 64 and 128 values): decoded tokens take the split-KV
     tensor-core kernel, prompt portions the tiled one, both with windows."""
