@@ -68,7 +68,7 @@ NX_B: Dict = model(320, 128, 4, 2e-6, [
     retention(4, 64, 32, (0.9, 0.99, 0.999, 0.96875), 32, base=500000.0, mlp=moe(8, 2, 64, 4, 2, scale=2.0)),
     latent(8, 16, 16, 64, 64, 48, 64, base=5000.0, mlp=moe(6, 1, 48, 6, 3)),
     channel_delta(4, 2, 64, 64, 4, 16, dense(192, 1.0)),
-    latent(2, 64, 64, 32, 32, 64, 130, base=20000.0),
+    latent(2, 64, 64, 32, 32, 64, 130, base=30000.0),
 ])
 
 # one stream; recurrent layers first (no paged cache before the last layer); all groups kept; one expert
