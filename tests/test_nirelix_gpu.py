@@ -486,6 +486,28 @@ def test_a_far_token_reaches_through_the_state(tmp_path, kind, dtype):
         nx.compare(run_engine(engine, reqs, schedule), want, tol, f"far token, {kind}, {cut} [{dtype}]")
 
 
+# ------------------------------------------------- long prompts at sizes between tiny and real
+LONG = nx.model(640, 256, 2, 1e-5, [
+    nx.latent(4, 32, 32, 64, 96, 96, 200, base=40000.0, mlp=nx.dense(512, 2.0)),
+    nx.channel_delta(4, 2, 64, 32, 4, 32, nx.moe(16, 4, 64, 4, 2, scale=2.5), gate_rank=16),
+    nx.retention(4, 32, 64, (0.9, 0.99, 0.999, 0.9995), 16, base=1e6, mlp=nx.dense(384, 1.5)),
+    nx.latent(2, 48, 16, 64, 64, 48, 64, base=500.0, mlp=nx.moe(8, 2, 96, 2, 1)),
+    nx.channel_delta(2, 2, 32, 64, 3, 24),
+])
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_long_prompts(tmp_path, dtype):
+    """Prompts of up to 1,500 tokens (two dozen pages of 64, windows of 200 and 64 that pass many of
+    them, cached rows of 128 and 64 values on the tensor-core kernels in bfloat16, states that forget
+    slowly), whole and in a mixed batch whose decoded tokens read hundreds of keys."""
+    state = nx.random_state(LONG, 7, slow_decay=True)
+    folder = nx.write(str(tmp_path / "m"), LONG, state)
+    reqs = {f"r{i}": nx.tokens(11 * i + 3, n, LONG["vocab"]) for i, n in enumerate([1500, 700, 64, 65, 129])}
+    for cut in ("whole", "mixed"):
+        run_and_compare(folder, LONG, state, reqs, CUTS[cut](reqs), dtype, 64, f"long {cut}")
+
+
 # --------------------------------------------------------- first tokens, long decoding
 @pytest.mark.parametrize("dtype", list(DTYPES))
 def test_first_tokens_and_long_decoding(models, dtype):
