@@ -168,8 +168,8 @@ def _read_latent(m: Any, where: str) -> LatentMixer:
                     window=int(_need(_need(m, "mask", where), "size", where + "mask.")), rot_base=base)
     _positive(where, heads=a.heads, dim=a.dim, vdim=a.vdim, q_rank=a.q_rank, kv_rank=a.kv_rank)
     _positive(where + "mask.", size=a.window)
-    if a.kv_rank + a.rot_dim > 512:
-        raise ConfigError(f"config.json: '{where}kv_rank' + rot_dim above 512 is not supported")
+    if a.kv_rank + a.rot_dim > 1024:
+        raise ConfigError(f"config.json: '{where}kv_rank' + rot_dim above 1024 is not supported")
     return a
 
 

@@ -106,7 +106,7 @@ extern "C" int ft_attn_paged_simt(const void* q, void* out, const void* kv_pages
                                   int table_width, int window, float scale, int dtype, int T,
                                   cudaStream_t stream) {
   if (T <= 0) return FT_OK;
-  if (d > 512 || d <= 0 || nkv <= 0 || nq % nkv) return FT_ERR_SHAPE;
+  if (d > 1024 || d <= 0 || nkv <= 0 || nq % nkv) return FT_ERR_SHAPE;
   AttnArgs a{q, out, kv_pages, token_pos, token_seg, block_table, rows, page_stride, kv_stride,
              nq, nkv, d, P, table_width, window, scale};
   dim3 grid(T, (nq + 3) / 4);
@@ -115,9 +115,12 @@ extern "C" int ft_attn_paged_simt(const void* q, void* out, const void* kv_pages
   if (d <= 256) {
     if (dtype == FT_DTYPE_F32) attn_paged_kernel<float, true, 8><<<grid, 128, smem, stream>>>(a);
     else attn_paged_kernel<__nv_bfloat16, false, 8><<<grid, 128, smem, stream>>>(a);
-  } else {                      // head sizes up to 512 (a latent that is wider than any head)
+  } else if (d <= 512) {        // a latent that is wider than any head
     if (dtype == FT_DTYPE_F32) attn_paged_kernel<float, true, 16><<<grid, 128, smem, stream>>>(a);
     else attn_paged_kernel<__nv_bfloat16, false, 16><<<grid, 128, smem, stream>>>(a);
+  } else {                      // up to 1024: a latent of 512 values and more with a rotated part behind it
+    if (dtype == FT_DTYPE_F32) attn_paged_kernel<float, true, 32><<<grid, 128, smem, stream>>>(a);
+    else attn_paged_kernel<__nv_bfloat16, false, 32><<<grid, 128, smem, stream>>>(a);
   }
   FT_LAUNCH_CHECK();
   return FT_OK;

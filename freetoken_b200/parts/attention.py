@@ -150,8 +150,8 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
         self.window = p.get("sliding_window")
         if self.nq % self.nkv:
             raise ValueError(f"num_heads {self.nq} is not a multiple of num_kv_heads {self.nkv}")
-        if self.d > 512:
-            raise ValueError(f"head size {self.d} exceeds what the attention kernels take (512)")
+        if self.d > 1024:
+            raise ValueError(f"head size {self.d} exceeds what the attention kernels take (1024)")
         if self.dk != self.dv and self.norm_mode:
             raise ValueError("a QK norm over heads that are filled up to the value size is not offered")
         pos_spec = p["position"]

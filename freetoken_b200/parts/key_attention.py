@@ -81,8 +81,8 @@ class SharedKVAttention(PagedSoftmaxCore, Mixer):
         self.window = p.get("sliding_window")
         if self.nkv <= 0 or self.nq % self.nkv:
             raise ValueError(f"num_heads {self.nq} is not a multiple of num_kv_heads {self.nkv}")
-        if self.d > 512:
-            raise ValueError(f"head_dim {self.d} exceeds what the attention kernels take (512)")
+        if self.d > 1024:
+            raise ValueError(f"head_dim {self.d} exceeds what the attention kernels take (1024)")
         if self.temp_coef != 0.0 and self.temp_every <= 0:
             raise ValueError("q_temp_every must be positive")
         names = p["names"]
@@ -168,8 +168,8 @@ class LatentAttention(PagedSoftmaxCore, Mixer):
                 raise ValueError(f"latent_attention: the position part turns {self.position.rotary_dim} "
                                  f"dimensions, the rotated key part has {self.rot}")
         self.full = bool(self.rot or self.q_rank or self.gate_per == "element")
-        if self.d > 512:
-            raise ValueError(f"latent rank plus rotated part {self.d} exceeds what the attention kernels take (512)")
+        if self.d > 1024:
+            raise ValueError(f"latent rank plus rotated part {self.d} exceeds what the attention kernels take (1024)")
         names = p["names"]
         scope = self.name(p["scope"])
         self.n = {k: f"{scope}.{v}" for k, v in names.items()}

@@ -319,6 +319,7 @@ ALONE = {
     "latent_attention": nx.one_layer(nx.latent(3, 8, 6, 10, 20, 14, 5)),
     "latent_attention_one_head_long_window": nx.one_layer(nx.latent(1, 4, 12, 20, 7, 30, 300, base=50.0), streams=1),
     "latent_attention_window_of_one": nx.one_layer(nx.latent(4, 10, 2, 3, 9, 5, 1, scale=0.7), streams=2),
+    "latent_attention_rows_wider_than_512": nx.one_layer(nx.latent(2, 8, 8, 6, 10, 520, 9), streams=2),
     "dense_feed_forward": nx.one_layer(nx.retention(1, 4, 4, (0.9,), 2, mlp=nx.dense(40, 0.7))),
     "routed_feed_forward": nx.one_layer(nx.retention(1, 4, 4, (0.9,), 2, mlp=nx.moe(8, 3, 16, 4, 2, scale=2.5))),
     "routed_feed_forward_top_one_no_groups": nx.one_layer(nx.retention(1, 4, 4, (0.9,), 2, mlp=nx.moe(4, 1, 16, 1, 1)), streams=1),
