@@ -12,6 +12,10 @@
 // Formula (python/freetoken/kernel/triton/attention.py:74,118-139): scores
 // q.k * scale for keys j <= pos (and j > pos - window when a window is set),
 // softmax over them, weighted sum of v; query head h reads KV head h / group.
+// Options no model of the reference has: a mask in chunks (a query sees the keys
+// of its own chunk of `chunk` positions, counted from position 0), scores capped
+// as cap * tanh(s / cap), and a sink - a score without key or value that enters
+// the softmax's denominator only, fixed (sink_mode 1) or one per query head (2).
 #include "common.cuh"
 
 namespace ft {
@@ -27,6 +31,11 @@ struct AttnArgs {
   long long page_stride, kv_stride;
   int nq, nkv, d, P, table_width, window;  // window <= 0: none
   float scale;
+  int chunk;              // > 0: keys of the query's own chunk of this many positions only
+  float softcap;          // > 0: score <- softcap * tanh(score / softcap)
+  int sink_mode;          // 0 none, 1 the score sink_value, 2 sink[h]
+  float sink_value;
+  const float* sink;      // [nq]
 };
 
 // MAXD: output dims per lane (head sizes up to 32 * MAXD)
@@ -46,7 +55,8 @@ __global__ void __launch_bounds__(128) attn_paged_kernel(AttnArgs a) {
 
   const int pos = a.token_pos[t];
   const int* table = a.block_table + (size_t)a.token_seg[t] * a.table_width;
-  const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  if (a.chunk > 0) lo = max(lo, pos - pos % a.chunk);
   const AT* kbase = (const AT*)a.kv_pages + (size_t)kvh * a.P * d;
   const AT* vbase = kbase + a.kv_stride;
 
@@ -65,6 +75,7 @@ __global__ void __launch_bounds__(128) attn_paged_kernel(AttnArgs a) {
       float dot = 0.f;
       for (int i = 0; i < d; ++i) dot = fmaf(qv[i], to_float(kr[i]), dot);
       s = dot * a.scale;
+      if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float p = valid ? (EXACT ? expf(s - m_new) : __expf(s - m_new)) : 0.f;
@@ -86,6 +97,16 @@ __global__ void __launch_bounds__(128) attn_paged_kernel(AttnArgs a) {
       }
     }
   }
+  if (a.sink_mode) {
+    // the sink joins the denominator once, after all keys (so the keys' order of summation
+    // does not depend on it)
+    const float sk = a.sink_mode == 2 ? a.sink[h] : a.sink_value;
+    const float m_new = fmaxf(m, sk);
+    const float alpha = EXACT ? expf(m - m_new) : __expf(m - m_new);
+    l = l * alpha + (EXACT ? expf(sk - m_new) : __expf(sk - m_new));
+#pragma unroll
+    for (int c = 0; c < MAXD; ++c) acc[c] *= alpha;
+  }
   AT* o = (AT*)a.out + ((size_t)t * a.nq + h) * d;
   const float inv = 1.f / l;
 #pragma unroll
@@ -104,11 +125,13 @@ extern "C" int ft_attn_paged_simt(const void* q, void* out, const void* kv_pages
                                   const int* block_table, const int* rows,
                                   long long page_stride, long long kv_stride, int nq, int nkv, int d, int P,
                                   int table_width, int window, float scale, int dtype, int T,
-                                  cudaStream_t stream) {
+                                  int chunk, float softcap, int sink_mode, float sink_value,
+                                  const float* sink, cudaStream_t stream) {
   if (T <= 0) return FT_OK;
   if (d > 1024 || d <= 0 || nkv <= 0 || nq % nkv) return FT_ERR_SHAPE;
   AttnArgs a{q, out, kv_pages, token_pos, token_seg, block_table, rows, page_stride, kv_stride,
-             nq, nkv, d, P, table_width, window, scale};
+             nq, nkv, d, P, table_width, window, scale, chunk, softcap, sink_mode, sink_value, sink};
+  if (sink_mode == 2 && !sink) return FT_ERR_SHAPE;
   dim3 grid(T, (nq + 3) / 4);
   const size_t smem = 4 * (size_t)d * sizeof(float);
   if (dtype != FT_DTYPE_F32 && dtype != FT_DTYPE_BF16) return FT_ERR_DTYPE;

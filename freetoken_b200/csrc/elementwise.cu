@@ -175,6 +175,8 @@ struct QkRopeArgs {
   int norm_mode;          // 0 none, 1 per layer, 2 per head
   int plus_one, interleaved;
   float eps;
+  int dn;                 // how many of a head's d values the norm's mean counts (the others are
+                          // zeros that fill a head up to d)
 };
 
 template <typename AT>
@@ -193,10 +195,10 @@ __global__ void qk_rope_store_kernel(QkRopeArgs a) {
   if (a.norm_mode == 1) {
     float s = 0.f;
     for (int i = threadIdx.x; i < qn; i += blockDim.x) { float x = to_float(q[i]); s += x * x; }
-    inv_q = rsqrtf(block_sum(s, scratch) / (float)qn + a.eps);
+    inv_q = rsqrtf(block_sum(s, scratch) / (float)(a.nq * a.dn) + a.eps);
     s = 0.f;
     for (int i = threadIdx.x; i < kn; i += blockDim.x) { float x = to_float(k[i]); s += x * x; }
-    inv_k = rsqrtf(block_sum(s, scratch) / (float)kn + a.eps);
+    inv_k = rsqrtf(block_sum(s, scratch) / (float)(a.nkv * a.dn) + a.eps);
   } else if (a.norm_mode == 2) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     for (int h = warp; h < a.nq + a.nkv; h += nwarps) {
@@ -204,7 +206,7 @@ __global__ void qk_rope_store_kernel(QkRopeArgs a) {
       float s = 0.f;
       for (int i = lane; i < a.d; i += 32) { float x = to_float(hp[i]); s += x * x; }
       s = warp_sum(s);
-      if (lane == 0) head_inv[h] = rsqrtf(s / (float)a.d + a.eps);
+      if (lane == 0) head_inv[h] = rsqrtf(s / (float)a.dn + a.eps);
     }
     __syncthreads();
   }
@@ -393,15 +395,15 @@ __global__ void __launch_bounds__(256) qk_rope_store_vec_kernel(QkRopeArgs a) {
     sum_pieces(row, qn >> 3, sq);
     sum_pieces(row + qn, kn >> 3, sk);
     block_sum2(sq, sk, scratch);
-    inv_q = rsqrtf(sq / (float)qn + a.eps);
-    inv_k = rsqrtf(sk / (float)kn + a.eps);
+    inv_q = rsqrtf(sq / (float)(a.nq * a.dn) + a.eps);
+    inv_k = rsqrtf(sk / (float)(a.nkv * a.dn) + a.eps);
   } else if (a.norm_mode == 2) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     for (int h = warp; h < a.nq + a.nkv; h += nwarps) {
       float s = 0.f;
       for (int c = lane; c < dc; c += 32) s += sumsq8(load8(row + (size_t)h * d + c * 8));
       s = warp_sum(s);
-      if (lane == 0) head_inv[h] = rsqrtf(s / (float)d + a.eps);
+      if (lane == 0) head_inv[h] = rsqrtf(s / (float)a.dn + a.eps);
     }
     __syncthreads();
   }
@@ -666,12 +668,13 @@ int ft_qk_rope_store(const void* qkv, void* q_out, void* kv_pages, const float* 
                      const int* token_seg, const int* block_table, long long ld,
                      long long page_stride, long long kv_stride, int nq, int nkv, int d, int R,
                      int P, int table_width, int norm_mode, int plus_one, int interleaved,
-                     float eps, int dtype, int T, cudaStream_t stream) {
+                     float eps, int dtype, int T, int norm_dim, cudaStream_t stream) {
   if (T <= 0) return FT_OK;
   if (R < 0 || R > d || (R & 1) || norm_mode < 0 || norm_mode > 2) return FT_ERR_SHAPE;
+  if (norm_dim <= 0 || norm_dim > d) norm_dim = d;
   QkRopeArgs a{qkv, q_out, kv_pages, q_weight, k_weight, cos_sin, token_pos, token_seg,
                block_table, ld, page_stride, kv_stride, nq, nkv, d, R, P, table_width,
-               norm_mode, plus_one, interleaved, eps};
+               norm_mode, plus_one, interleaved, eps, norm_dim};
   const size_t smem = (size_t)(nq + nkv) * sizeof(float);
   const bool aligned = !((uintptr_t)qkv & 15) && !((uintptr_t)q_out & 15) &&
                        !((uintptr_t)kv_pages & 15) && !(ld & 7) && !(page_stride & 7) &&

@@ -154,8 +154,10 @@ def qk_rope_store(qkv: torch.Tensor, q_out: torch.Tensor, kv_pages: Optional[tor
                   cos_sin: Optional[torch.Tensor], token_pos: torch.Tensor,
                   token_seg: torch.Tensor, block_table: torch.Tensor, num_heads: int,
                   num_kv_heads: int, head_dim: int, rotary_dim: int, norm_mode: int,
-                  plus_one: bool, interleaved: bool, eps: float) -> None:
+                  plus_one: bool, interleaved: bool, eps: float, norm_dim: int = 0) -> None:
     """QK norm (0 none, 1 per layer, 2 per head), partial rotary, K/V page store.
+    ``norm_dim`` (0: ``head_dim``): how many of a head's values the norm's mean counts, where
+    query and key heads were filled up with zeros to ``head_dim``.
 
     ``kv_pages`` is ``[2, pages, kv_heads, page_size, head_dim]`` or ``None``
     for a stop that reads another stop's cache."""
@@ -187,12 +189,12 @@ def qk_rope_store(qkv: torch.Tensor, q_out: torch.Tensor, kv_pages: Optional[tor
         if cos_sin.shape[1] != rotary_dim:
             raise KernelError("qk_rope_store: cos_sin table width differs from rotary_dim")
     f = _fn("elementwise", "ft_qk_rope_store",
-            "p p p p p p p p p q q q i i i i i i i i i f i i")
+            "p p p p p p p p p q q q i i i i i i i i i f i i i")
     _check(f(_ptr(qkv), _ptr(q_out), _ptr(kv_pages), _ptr(q_weight), _ptr(k_weight),
              _ptr(cos_sin) if rotary_dim else None, _ptr(token_pos), _ptr(token_seg),
              _ptr(block_table), qkv.stride(0), page_stride, kv_stride, num_heads, num_kv_heads,
              head_dim, rotary_dim, P, block_table.shape[1], norm_mode, int(plus_one),
-             int(interleaved), float(eps), code(qkv.dtype), T, _stream()), "qk_rope_store")
+             int(interleaved), float(eps), code(qkv.dtype), T, int(norm_dim), _stream()), "qk_rope_store")
 
 
 def combine(parts: torch.Tensor, out: torch.Tensor, k: int) -> None:
@@ -241,6 +243,38 @@ def embed_norm(ids: torch.Tensor, table: torch.Tensor, weight: torch.Tensor, res
     f = _fn("rowwise", "ft_embed_norm", "p p i p p i i i f")
     _check(f(_ptr(ids), _ptr(table), code(table.dtype), _ptr(weight), _ptr(residual), T, H, table.shape[0],
              float(eps), _stream()), "embed_norm")
+
+
+def embed_pair(ids: torch.Tensor, token_pos: torch.Tensor, token_seg: torch.Tensor, seg_slot: torch.Tensor,
+               seg_q_start: torch.Tensor, table: torch.Tensor, pair_table: Optional[torch.Tensor],
+               last_token: Optional[torch.Tensor], residual: torch.Tensor, scale: float, buckets: int = 0,
+               mul_prev: int = 0, mul_cur: int = 0) -> None:
+    """residual[t] = table[ids[t]] * scale + pair_table[row_t] in float32, written to every stream of
+    a ``[T, copies, H]`` residual.  ``row_t = (previous token * mul_prev + ids[t] * mul_cur) mod
+    buckets``; a sequence's first token (position 0) takes row ``buckets``.  ``last_token``
+    (``[slots, >= 1]`` int32) carries each request's last token from step to step: read for a
+    portion's first token, then set to the portion's last.  ``pair_table`` None: only the scale."""
+    _need(ids, "ids", torch.int32)
+    _need(table, "table")
+    _need(residual, "residual", torch.float32)
+    T, H = residual.shape[0], residual.shape[-1]
+    copies = residual.shape[1] if residual.dim() == 3 else 1
+    if table.shape[1] != H or ids.numel() != T or residual.dim() not in (2, 3):
+        raise KernelError("embed_pair: shapes do not match")
+    stride = 0
+    if pair_table is not None:
+        _need(pair_table, "pair_table", table.dtype)
+        _need(last_token, "last_token", torch.int32, contiguous=False)
+        if pair_table.shape != (buckets + 1, H) or buckets < 1 or last_token.dim() != 2:
+            raise KernelError("embed_pair: the second table has buckets + 1 rows of the embedding's width")
+        stride = last_token.stride(0)
+        for name, t in (("token_pos", token_pos), ("token_seg", token_seg), ("seg_slot", seg_slot),
+                        ("seg_q_start", seg_q_start)):
+            _need(t, name, torch.int32)
+    f = _fn("rowwise", "ft_embed_pair", "p p p p p p p p p q q q i i i i f i i")
+    _check(f(_ptr(ids), _ptr(token_pos), _ptr(token_seg), _ptr(seg_slot), _ptr(seg_q_start), _ptr(table),
+             _ptr(pair_table), _ptr(last_token), _ptr(residual), stride, int(mul_prev), int(mul_cur), int(buckets),
+             H, table.shape[0], copies, float(scale), code(table.dtype), T, _stream()), "embed_pair")
 
 
 def key_store(src: torch.Tensor, q_out: Optional[torch.Tensor], pages: Optional[torch.Tensor],
@@ -472,9 +506,10 @@ def latent_store(down: torch.Tensor, q: torch.Tensor, q_abs: torch.Tensor, pages
 # ------------------------------------------------------- mixers with a carried state
 def conv_silu(x: torch.Tensor, out: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
               state: torch.Tensor, token_seg: torch.Tensor, seg_slot: torch.Tensor,
-              seg_q_start: torch.Tensor) -> None:
+              seg_q_start: torch.Tensor, activation: bool = True) -> None:
     """A causal convolution over time per channel, then SiLU: ``out[t, c] = silu(bias[c] +
-    sum_j weight[c, j] * u[t - (taps - 1) + j, c])`` where ``u`` is the request's inputs so far.
+    sum_j weight[c, j] * u[t - (taps - 1) + j, c])`` where ``u`` is the request's inputs so far
+    (``activation=False``: the sum itself, no SiLU).
     ``x`` ``[T, C]`` (a column range of a wider matrix is fine), ``state`` ``[slots, >= (taps - 1) *
     C]`` float32: a request's last ``taps - 1`` inputs, read first and then brought up to date."""
     _need(x, "x", contiguous=False)
@@ -493,10 +528,10 @@ def conv_silu(x: torch.Tensor, out: torch.Tensor, weight: torch.Tensor, bias: Op
         _need(t, name, torch.int32)
     global LAUNCHES
     LAUNCHES += 1 if taps > 1 else 0
-    f = _fn("recurrent", "ft_conv_silu", "p q p q p p p q p p p i i i i i")
+    f = _fn("recurrent", "ft_conv_silu", "p q p q p p p q p p p i i i i i i")
     _check(f(_ptr(x), x.stride(0), _ptr(out), out.stride(0), _ptr(weight), _ptr(bias), _ptr(state),
              state.stride(0), _ptr(token_seg), _ptr(seg_slot), _ptr(seg_q_start), C, taps, T,
-             seg_slot.numel(), code(x.dtype), _stream()), "conv_silu")
+             seg_slot.numel(), code(x.dtype), int(activation), _stream()), "conv_silu")
 
 
 def ssd_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
@@ -904,10 +939,46 @@ def pass_rows(rows: int) -> int:
 
 
 # ------------------------------------------------------------- attention
+class ScoreOptions:
+    """What a softmax attention may do to its scores beyond scale and window, as every attention
+    kernel takes it: ``chunk`` (> 0: a query sees the keys of its own chunk of that many positions,
+    counted from position 0), ``softcap`` (> 0: ``s <- softcap * tanh(s / softcap)``), and a sink -
+    a score without key or value that enters the softmax's denominator only: ``sink_value`` (a
+    fixed score) or ``sink`` (float32, one learned score per query head)."""
+
+    __slots__ = ("chunk", "softcap", "sink_value", "sink")
+
+    def __init__(self, chunk: int = 0, softcap: float = 0.0, sink_value: Optional[float] = None,
+                 sink: Optional[torch.Tensor] = None):
+        self.chunk, self.softcap = int(chunk or 0), float(softcap or 0.0)
+        self.sink_value, self.sink = sink_value, sink
+        if sink is not None and sink_value is not None:
+            raise KernelError("a sink is a fixed score or one per head, not both")
+
+    @property
+    def sink_mode(self) -> int:
+        return 2 if self.sink is not None else (1 if self.sink_value is not None else 0)
+
+    def plain(self) -> bool:
+        return not (self.chunk or self.softcap or self.sink_mode)
+
+    def args(self, num_heads: int):
+        """``(chunk, softcap, sink_mode, sink_value, sink pointer)`` as the launchers take them."""
+        if self.sink is not None:
+            _need(self.sink, "sink", torch.float32)
+            if self.sink.numel() != num_heads:
+                raise KernelError("the sink has one score per query head")
+        return (self.chunk, self.softcap, self.sink_mode, float(self.sink_value or 0.0), _ptr(self.sink))
+
+
+NO_SCORE_OPTIONS = ScoreOptions()
+
+
 def attn_paged_simt(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
                     token_pos: torch.Tensor, token_seg: torch.Tensor, block_table: torch.Tensor,
                     num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                    window: Optional[int], rows: Optional[torch.Tensor] = None) -> None:
+                    window: Optional[int], rows: Optional[torch.Tensor] = None,
+                    options: Optional[ScoreOptions] = None) -> None:
     """Generic paged attention; ``rows`` limits it to those token rows."""
     _need(q, "q")
     _need(out, "out", q.dtype)
@@ -919,11 +990,11 @@ def attn_paged_simt(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
         _need(rows, "rows", torch.int32)
     if q.shape[1] != num_heads * head_dim or out.shape != q.shape:
         raise KernelError("attn_paged_simt: q/out must be [T, heads*head_dim]")
-    f = _fn("attention_simt", "ft_attn_paged_simt", "p p p p p p p q q i i i i i i f i i")
+    f = _fn("attention_simt", "ft_attn_paged_simt", "p p p p p p p q q i i i i i i f i i i f i f p")
     _check(f(_ptr(q), _ptr(out), _ptr(kv_pages), _ptr(token_pos), _ptr(token_seg),
              _ptr(block_table), _ptr(rows), kv_pages.stride(1), kv_pages.stride(0), num_heads, num_kv_heads,
              head_dim, kv_pages.shape[3], block_table.shape[1], int(window or 0), float(scale),
-             code(q.dtype), T, _stream()), "attn_paged_simt")
+             code(q.dtype), T, *(options or NO_SCORE_OPTIONS).args(num_heads), _stream()), "attn_paged_simt")
 
 
 DECODE_HEAD_DIMS = (32, 64, 128)

@@ -69,6 +69,7 @@ struct ConvArgs {
   const int* seg_q_start;  // [S + 1]
   long long ldx, ldo, slot_stride;
   int C, taps;
+  int act;              // 1: SiLU behind the sum; 0: the sum itself
 };
 
 constexpr int CONV_MAX_TAPS = 8;     // longer convolutions take the plain loop
@@ -158,7 +159,7 @@ __global__ void __launch_bounds__(128) conv_silu_kernel(ConvArgs a, int T) {
 #pragma unroll
       for (int j = 0; j < CONV_MAX_TAPS; ++j)
         if (j <= K) acc = fmaf(w[u][j], win[u][j], acc);
-      out[u] = silu_f(acc + bias[u]);
+      out[u] = a.act ? silu_f(acc + bias[u]) : acc + bias[u];
     }
     AT* o = (AT*)a.out + (size_t)t * a.ldo + c;
     if constexpr (CPT == 2) *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(out[0], out[1]);
@@ -185,7 +186,7 @@ __global__ void __launch_bounds__(128) conv_silu_long_kernel(ConvArgs a) {
     acc = fmaf(a.w[(size_t)c * a.taps + j], v, acc);
   }
   if (a.bias) acc += a.bias[c];
-  ((AT*)a.out)[(size_t)t * a.ldo + c] = from_float<AT>(silu_f(acc));
+  ((AT*)a.out)[(size_t)t * a.ldo + c] = from_float<AT>(a.act ? silu_f(acc) : acc);
 }
 
 // After the convolution has read it: the slot keeps the last taps-1 inputs of (what it held ++
@@ -850,10 +851,10 @@ extern "C" {
 // Both kernels of the short convolution: outputs first, then the slots' new contents.
 int ft_conv_silu(const void* x, long long ldx, void* out, long long ldo, const float* w, const float* bias,
                  float* state, long long slot_stride, const int* token_seg, const int* seg_slot,
-                 const int* seg_q_start, int C, int taps, int T, int S, int dtype, cudaStream_t stream) {
+                 const int* seg_q_start, int C, int taps, int T, int S, int dtype, int act, cudaStream_t stream) {
   if (T <= 0 || S <= 0) return FT_OK;
   if (C <= 0 || taps < 1) return FT_ERR_SHAPE;
-  ConvArgs a{x, out, w, bias, state, token_seg, seg_slot, seg_q_start, ldx, ldo, slot_stride, C, taps};
+  ConvArgs a{x, out, w, bias, state, token_seg, seg_slot, seg_q_start, ldx, ldo, slot_stride, C, taps, act};
   const int cb = (C + 127) / 128;
   if (taps > CONV_MAX_TAPS) {
     FT_DISPATCH(dtype, AT, launch_pdl(conv_silu_long_kernel<AT>, dim3(T, cb), dim3(128), 0, stream, a));

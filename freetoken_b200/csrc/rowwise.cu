@@ -7,6 +7,7 @@
 // launch.
 //
 //   embed_norm      r[t,:] = rms(E[id_t,:]) * g          (gather + RMS norm in one pass)
+//   embed_pair      r[t,:] = E[id_t,:] * scale + B[hash(id_{t-1}, id_t),:]
 //   key_store       q_out[t,h,:] = q[t,h,:] * (1 + coef * ln(floor((p_t + 1) / every) + 1))
 //                   k[t,g,:] -> (optionally rms(k) * w, per key head) -> page of p_t
 //   gate_heads      o[t,h,:] *= sigmoid(z[t,h])
@@ -685,11 +686,81 @@ __global__ void __launch_bounds__(128) latent_store_kernel(LatentStoreArgs a) {
   for (int i = threadIdx.x; i < half; i += blockDim.x) turn(down + a.rank, dst + a.rank, i);
 }
 
+
+// ------------------------------------------------- embedding with a second, hashed table
+// r[t,:] = E[id_t,:] * scale + B[row_t,:] where row_t = (prev_t * mul_prev + id_t * mul_cur) mod
+// buckets and prev_t is the token before t in its sequence; a sequence's first token takes row
+// `buckets`, the table's last.  The token before a portion's first token is what the request's
+// slot carries (one int32 a slot); the block of a portion's first token reads it and then leaves
+// the portion's last token there, so nobody else touches the slot in this launch.  The sum is
+// float32 and is written to every one of `copies` residual streams.
+struct EmbedPairArgs {
+  const int* ids;          // [T]
+  const int* token_pos;    // [T]
+  const int* token_seg;    // [T]
+  const int* seg_slot;     // [S]
+  const int* seg_q_start;  // [S + 1]
+  const void* table;       // [vocab, H]
+  const void* pair_table;  // [buckets + 1, H], or nullptr: no second table
+  int* last_token;         // slot s: last_token[s * slot_stride]
+  float* residual;         // [T, copies, H]
+  long long slot_stride;
+  long long mul_prev, mul_cur;
+  int buckets, H, vocab, copies;
+  float scale;
+};
+
+template <typename WT>
+__global__ void __launch_bounds__(256) embed_pair_kernel(EmbedPairArgs a) {
+  pdl_wait();
+  const int t = blockIdx.x;
+  int id = a.ids[t];
+  if (id < 0 || id >= a.vocab) id = 0;  // validated on the host; never index outside the table
+  const WT* row = (const WT*)a.table + (size_t)id * a.H;
+  const WT* pair = nullptr;
+  if (a.pair_table) {
+    const int seg = a.token_seg[t];
+    const int q0 = a.seg_q_start[seg];
+    long long r = a.buckets;
+    if (a.token_pos[t] > 0) {
+      int prev = t > q0 ? a.ids[t - 1] : a.last_token[(size_t)a.seg_slot[seg] * a.slot_stride];
+      if (prev < 0 || prev >= a.vocab) prev = 0;
+      r = ((long long)prev * a.mul_prev + (long long)id * a.mul_cur) % a.buckets;
+      if (r < 0) r += a.buckets;
+    }
+    pair = (const WT*)a.pair_table + (size_t)r * a.H;
+    if (t == q0) {
+      // all threads have read the slot (or will not): the slot's new content is this portion's last token
+      __syncthreads();
+      if (threadIdx.x == 0) a.last_token[(size_t)a.seg_slot[seg] * a.slot_stride] = a.ids[a.seg_q_start[seg + 1] - 1];
+    }
+  }
+  float* out = a.residual + (size_t)t * a.H * a.copies;
+  for (int i = threadIdx.x; i < a.H; i += blockDim.x) {
+    float v = to_float(row[i]) * a.scale;
+    if (pair) v += to_float(pair[i]);
+    for (int c = 0; c < a.copies; ++c) out[(size_t)c * a.H + i] = v;
+  }
+}
+
 }  // namespace ft
 
 using namespace ft;
 
 extern "C" {
+
+int ft_embed_pair(const int* ids, const int* token_pos, const int* token_seg, const int* seg_slot,
+                  const int* seg_q_start, const void* table, const void* pair_table, int* last_token,
+                  float* residual, long long slot_stride, long long mul_prev, long long mul_cur, int buckets,
+                  int H, int vocab, int copies, float scale, int table_dtype, int T, cudaStream_t stream) {
+  if (T <= 0) return FT_OK;
+  if (copies < 1 || (pair_table && (buckets < 1 || !last_token))) return FT_ERR_SHAPE;
+  EmbedPairArgs a{ids, token_pos, token_seg, seg_slot, seg_q_start, table, pair_table, last_token, residual,
+                  slot_stride, mul_prev, mul_cur, buckets, H, vocab, copies, scale};
+  FT_DISPATCH(table_dtype, WT, launch_pdl(embed_pair_kernel<WT>, dim3(T), dim3(256), 0, stream, a));
+  FT_LAUNCH_CHECK();
+  return FT_OK;
+}
 
 int ft_embed_norm(const int* ids, const void* table, int table_dtype, const float* weight, float* residual,
                   int T, int H, int vocab, float eps, cudaStream_t stream) {

@@ -138,6 +138,10 @@ class Engine:
         for i, stop in enumerate(self.plan.schedule):
             owner = self.plan.cache_owner(i)
             self.cache_views.append(self._cache_view(owner, needs[owner], writes=(owner == i)))
+        if len(needs) > len(self.plan.schedule):
+            # the embedding's per-request state, behind the stops' views
+            at = len(self.plan.schedule)
+            self.cache_views.append(self._cache_view(at, needs[at], writes=True))
         self._pinned: List[torch.Tensor] = []
         self._pinned_events: List[torch.cuda.Event] = []
         self._pinned_turn = 0

@@ -123,11 +123,14 @@ class Model:
     # ---- cache -------------------------------------------------------------
     def cache_needs(self) -> List[Optional[CacheNeed]]:
         """Per stop of the schedule: what the cache manager keeps for it
-        (``None`` for stops that keep nothing or read another stop's cache)."""
+        (``None`` for stops that keep nothing or read another stop's cache).  An embedding that
+        keeps something per request adds one entry behind the stops'."""
         needs: List[Optional[CacheNeed]] = []
         for stop in self.plan.schedule:
             need = self.blocks[stop.layer].mixer.cache_need() if stop.owns_cache else None
             needs.append(need)
+        if self.embedding.cache_need() is not None:
+            needs.append(self.embedding.cache_need())
         return needs
 
     # ---- forward ------------------------------------------------------------
@@ -136,13 +139,17 @@ class Model:
                 all_rows_in_order: bool = False) -> torch.Tensor:
         """Run the step's tokens; write float32 logits of ``logit_rows`` into
         ``logits`` ``[len(logit_rows), vocab]``.  ``all_rows_in_order`` says
-        that ``logit_rows`` is ``0..T-1``, which saves the row gather."""
+        that ``logit_rows`` is ``0..T-1``, which saves the row gather.  ``caches`` holds a view
+        per stop and, behind them, the embedding's if it has a cache need."""
         T = ctx.num_tokens
         H = self.plan.hidden_size
         streams = self.plan.residual_streams
         # several residual streams per token start out as copies of the embedded row
         residual = ctx.workspace.get("model.residual", (T, H) if streams == 1 else (T, streams, H), torch.float32)
-        self.embedding.forward(ctx, residual)
+        if len(caches) > len(self.plan.schedule):
+            self.embedding.forward(ctx, residual, caches[len(self.plan.schedule)])
+        else:
+            self.embedding.forward(ctx, residual)
         delta = None
         for stop, cache in zip(self.plan.schedule, caches):
             delta = self.blocks[stop.layer].forward(ctx, delta, residual, cache)

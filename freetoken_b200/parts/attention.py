@@ -6,6 +6,13 @@ RMSNorm (over the whole q / k projection, or per head), rotary on the first
 causal softmax attention with scale ``sm_scale`` over the cached keys (all of
 them, or the latest ``sliding_window``), then ``@ Wo^T``.
 
+Options no model of the reference has, each a parameter of the mixer: a short causal
+convolution per channel behind the q, k and v projections (its last inputs per request in a
+state slot); a mask in chunks (a query sees the keys of its own chunk of positions); scores
+capped by ``cap * tanh(s / cap)``; a sink in the softmax's denominator, a fixed score or a
+learned one per head; a sigmoid gate on the heads' outputs, one per head or one per value, read
+from the mixer's input by the same merged product.
+
 Reference: python/freetoken/models/minimax_m2/attention.py:29-84 (merged QKV,
 per-layer norm, rotary, backend call, o_proj),
 python/freetoken/models/minimax_m3/attention.py:54-56,90-92 (per-head norm),
@@ -21,7 +28,7 @@ from typing import Dict, List
 import numpy as np
 import torch
 
-from ..cache.manager import PagedKVNeed
+from ..cache.manager import CompositeNeed, PagedKVNeed, StateNeed
 from ..csrc import ops
 from ..weights.spec import Cat, Init, Name, TensorSpec
 from . import linear
@@ -44,6 +51,8 @@ class PagedSoftmaxCore:
     d: int
     scale: float
     window = None
+    # what else happens to the scores (chunks, cap, sink): ops.ScoreOptions, None: nothing
+    options = None
 
     # ---- step metadata ---------------------------------------------------------
     def step_plan_key(self):
@@ -93,7 +102,7 @@ class PagedSoftmaxCore:
         longer segments to a prefill kernel; sizes those refuse (and the
         float32 path) go to the generic kernel.  ``kv_pages`` is ``[2 (K, V),
         pages, kv_heads, page, head_dim]``."""
-        if ops.attn_decode_takes(q, self.d):
+        if ops.attn_decode_takes(q, self.d) and (self.options is None or self.options.plain()):
             plan = ctx.plan(self)
             n_dec, n_tiles = plan.host["num_decode_rows"], plan.host["num_prefill_tiles"]
             if n_dec > 0:
@@ -111,7 +120,7 @@ class PagedSoftmaxCore:
                                  table, self.nq, self.nkv, self.d, self.scale, self.window)
             return
         ops.attn_paged_simt(q, o, kv_pages, ctx.token_pos, ctx.token_seg, table,
-                            self.nq, self.nkv, self.d, self.scale, self.window)
+                            self.nq, self.nkv, self.d, self.scale, self.window, options=self.options)
 
 
 @register_mixer("paged_attention")
@@ -128,7 +137,17 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
     the weights are bound, which changes no score and no output and costs cache and
     arithmetic only where the two sizes differ.  ``bias`` (default False): the q, k, v and o
     projections add a bias (``checkpoint_names`` then also has q_bias, k_bias, v_bias, o_bias
-    and the fused qkv_bias)."""
+    and the fused qkv_bias).
+
+    ``conv_taps`` (default 0): q, k and v each pass a causal convolution over time per channel
+    (``checkpoint_names`` q_conv, k_conv, v_conv: ``[channels, taps]``, the last column weighing
+    the current token; no bias, no activation) directly behind the projection; the last
+    ``conv_taps - 1`` projected rows of a request live in a state slot.  ``chunk``: a query sees
+    only keys of its own chunk of that many positions.  ``softcap``: scores become ``cap *
+    tanh(score / cap)``.  ``sink_value`` (a fixed score) or ``sink`` (True: a learned score per
+    head, ``checkpoint_names`` sink): a score without key or value in the softmax's denominator.
+    ``gate`` (``"head"`` or ``"element"``): the heads' outputs times ``sigmoid(Wg x)``, one gate
+    per head or per value (``checkpoint_names`` gate), merged into the qkv product."""
 
     graph_capturable = True
     writes_into_out = True
@@ -148,12 +167,24 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
         self.norm_eps = float(p.get("qk_norm_eps", 1e-6))
         self.norm_plus_one = bool(p.get("qk_norm_plus_one", False))
         self.window = p.get("sliding_window")
+        self.chunk = int(p.get("chunk") or 0)
+        self.softcap = float(p.get("softcap") or 0.0)
+        self.sink_value = p.get("sink_value")
+        self.learned_sink = bool(p.get("sink", False))
+        self.gate = p.get("gate")
+        self.taps = int(p.get("conv_taps") or 0)
+        if self.gate not in (None, "head", "element"):
+            raise ValueError("gate must be None, 'head' or 'element'")
+        if self.window and self.chunk:
+            raise ValueError("a sliding window and a mask in chunks exclude each other")
+        if self.learned_sink and self.sink_value is not None:
+            raise ValueError("a sink is a fixed score or a learned one per head, not both")
         if self.nq % self.nkv:
             raise ValueError(f"num_heads {self.nq} is not a multiple of num_kv_heads {self.nkv}")
         if self.d > 1024:
             raise ValueError(f"head size {self.d} exceeds what the attention kernels take (1024)")
-        if self.dk != self.dv and self.norm_mode:
-            raise ValueError("a QK norm over heads that are filled up to the value size is not offered")
+        if self.dk != self.dv and self.norm_plus_one and self.dk < self.d:
+            raise ValueError("a one-plus QK norm over heads that are filled up to the value size is not offered")
         pos_spec = p["position"]
         self.position = POSITIONS.get(pos_spec.kind)(pos_spec, prefix)
         scope = p["scope"]
@@ -165,6 +196,14 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
         self.n_knorm = f"{self.scope}.{names['k_norm']}"
         self._split = [f"{self.scope}.{names[k]}" for k in ("q", "k", "v")]
         self.w_qkv = self.w_o = self.w_qnorm = self.w_knorm = self.b_qkv = self.b_o = None
+        self.n_gate = f"{self.scope}.{names['gate']}" if self.gate else None
+        self.n_sink = f"{self.scope}.{names['sink']}" if self.learned_sink else None
+        self.n_conv = f"{self.scope}.{names.get('qkv_conv', 'qkv.conv')}" if self.taps else None
+        self._split_conv = [f"{self.scope}.{names[k]}" for k in ("q_conv", "k_conv", "v_conv")] if self.taps else []
+        self.w_conv = self.w_sink = None
+        self.gate_width = 0 if not self.gate else (self.nq if self.gate == "head" else self.nq * self.dv)
+        if self.gate and self.has_bias:
+            raise ValueError("a gate merged into a biased qkv product is not offered")
         if self.has_bias:
             self.n_qkv_bias = f"{self.scope}.{names['qkv_bias']}"
             self.n_o_bias = f"{self.scope}.{names['o_bias']}"
@@ -175,24 +214,38 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
 
     # ---- cache and weights ------------------------------------------------
     def cache_need(self):
-        return PagedKVNeed(self.nkv, self.d, self.window)
+        # keys of chunks that are over are never read again: the pages behind the last `chunk`
+        # positions go back to the pool like those behind a window
+        paged = PagedKVNeed(self.nkv, self.d, self.window or (self.chunk or None))
+        if self.taps > 1:
+            return CompositeNeed((paged, StateNeed(((self.taps - 1) * (self.nq + 2 * self.nkv) * self.d,))))
+        return paged
 
     def tensor_specs(self) -> List[TensorSpec]:
         qn, kn, vn = self.nq * self.dk, self.nkv * self.dk, self.nkv * self.dv
+        pieces = [Name(self._split[0], (qn, self.hidden)), Name(self._split[1], (kn, self.hidden)),
+                  Name(self._split[2], (vn, self.hidden))]
+        if self.gate:
+            pieces.append(Name(self.n_gate, (self.gate_width, self.hidden)))
         specs = [
-            TensorSpec(self.n_qkv, (qn + kn + vn, self.hidden), sources=(Cat((
-                Name(self._split[0], (qn, self.hidden)),
-                Name(self._split[1], (kn, self.hidden)),
-                Name(self._split[2], (vn, self.hidden))), 0),)),
+            TensorSpec(self.n_qkv, (qn + kn + vn + self.gate_width, self.hidden), sources=(Cat(tuple(pieces), 0),)),
             TensorSpec(self.n_o, (self.hidden, self.nq * self.dv), tag="residual_out"),
         ]
+        if self.taps:
+            specs.append(TensorSpec(self.n_conv, (qn + kn + vn, self.taps), role="small32",
+                                    init=Init(mean=0.0, std=self.taps ** -0.5), tag="conv", sources=(Cat((
+                                        Name(self._split_conv[0], (qn, self.taps)),
+                                        Name(self._split_conv[1], (kn, self.taps)),
+                                        Name(self._split_conv[2], (vn, self.taps))), 0),)))
+        if self.learned_sink:
+            specs.append(TensorSpec(self.n_sink, (self.nq,), role="small32", init=Init(mean=0.0, std=1.0), tag="sink"))
         if self.has_bias:
             specs.append(TensorSpec(self.n_qkv_bias, (qn + kn + vn,), role="small32", tag="bias", sources=(Cat((
                 Name(self._split_bias[0], (qn,)), Name(self._split_bias[1], (kn,)),
                 Name(self._split_bias[2], (vn,))), 0),)))
             specs.append(TensorSpec(self.n_o_bias, (self.hidden,), role="small32", tag="bias"))
         if self.norm_mode:
-            sizes = (qn, kn) if self.norm_mode == 1 else (self.d, self.d)
+            sizes = (qn, kn) if self.norm_mode == 1 else (self.dk, self.dk)
             mean = 0.0 if self.norm_plus_one else 1.0
             for name, size in zip((self.n_qnorm, self.n_knorm), sizes):
                 specs.append(TensorSpec(name, (size,), role="small32",
@@ -218,24 +271,54 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
 
     def bind(self, tensors: Dict[str, torch.Tensor], dtype) -> None:
         runs = ((self.nq, self.dk), (self.nkv, self.dk), (self.nkv, self.dv))
-        self.w_qkv = self._filled(tensors[self.n_qkv], runs, 0)
+        gate_runs = () if not self.gate else (((self.nq, 1),) if self.gate == "head" else ((self.nq, self.dv),))
+        if self.gate == "head":
+            # one row per head: not a head's worth of values, nothing to fill up
+            w = tensors[self.n_qkv]
+            self.w_qkv = torch.cat((self._filled(w[:w.shape[0] - self.nq], runs, 0), w[w.shape[0] - self.nq:]), 0).contiguous()
+        else:
+            self.w_qkv = self._filled(tensors[self.n_qkv], runs + gate_runs, 0)
         self.w_o = self._filled(tensors[self.n_o], ((self.nq, self.dv),), 1)
         if self.has_bias:
             self.b_qkv = self._filled(tensors[self.n_qkv_bias], runs, 0)
             self.b_o = tensors[self.n_o_bias]
-        if self.norm_mode:
-            self.w_qnorm = tensors[self.n_qnorm]
-            self.w_knorm = tensors[self.n_knorm]
+        if self.norm_mode == 1:
+            self.w_qnorm = self._filled(tensors[self.n_qnorm], ((self.nq, self.dk),), 0)
+            self.w_knorm = self._filled(tensors[self.n_knorm], ((self.nkv, self.dk),), 0)
+        elif self.norm_mode:
+            self.w_qnorm = self._filled(tensors[self.n_qnorm], ((1, self.dk),), 0)
+            self.w_knorm = self._filled(tensors[self.n_knorm], ((1, self.dk),), 0)
+        if self.taps:
+            self.w_conv = self._filled(tensors[self.n_conv], runs, 0)
+        if self.learned_sink:
+            self.w_sink = tensors[self.n_sink]
+        if self.chunk or self.softcap or self.learned_sink or self.sink_value is not None:
+            self.options = ops.ScoreOptions(self.chunk, self.softcap, self.sink_value, self.w_sink)
 
     def libraries(self, dtype) -> List[str]:
-        return ["elementwise"] + self.attention_libraries(dtype) + linear.libraries(dtype, self.has_bias)
+        return (["elementwise"] + self.attention_libraries(dtype) + linear.libraries(dtype, self.has_bias)
+                + (["recurrent"] if self.taps else []) + (["rowwise"] if self.gate else []))
 
     # ---- forward ----------------------------------------------------------------
     def forward(self, ctx: StepContext, x: torch.Tensor, cache: CacheView, out=None) -> torch.Tensor:
         T = x.shape[0]
         ws = ctx.workspace
         qn, kn = self.nq * self.d, self.nkv * self.d
-        qkv = linear.linear(x, self.w_qkv, ws.get("attn.qkv", (T, qn + 2 * kn), ctx.dtype), bias=self.b_qkv)
+        gw = self.gate_width if self.gate == "head" else (qn if self.gate else 0)
+        qkv = linear.linear(x, self.w_qkv, ws.get("attn.qkv", (T, qn + 2 * kn + gw), ctx.dtype), bias=self.b_qkv)
+        gate = qkv[:, qn + 2 * kn:] if self.gate else None
+        if self.gate:
+            qkv = qkv[:, :qn + 2 * kn]
+        if self.taps > 1:
+            cache, conv = cache.members
+            mixed = ws.get("attn.conv", (T, qn + 2 * kn), ctx.dtype)
+            if not cache.writes:
+                raise ValueError("a mixer with a convolution's state cannot read another stop's cache")
+            ops.conv_silu(qkv, mixed, self.w_conv, None, conv.state, ctx.token_seg, ctx.seg_slot, ctx.seg_q_start,
+                          activation=False)
+            qkv = mixed
+        elif self.taps == 1:
+            raise ValueError("a convolution of one tap is a factor per channel: fold it into the projection")
         q = ws.get("attn.q", (T, qn), ctx.dtype)
         table = ctx.block_tables[cache.block_table_index]
         cos_sin = self.position.table(ctx.device, ctx.max_positions)
@@ -243,9 +326,13 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
             qkv, q, cache.kv_pages if cache.writes else None, self.w_qnorm, self.w_knorm,
             cos_sin, ctx.token_pos, ctx.token_seg, table, self.nq, self.nkv, self.d,
             self.position.rotary_dim, self.norm_mode, self.norm_plus_one,
-            self.position.interleaved, self.norm_eps)
+            self.position.interleaved, self.norm_eps, norm_dim=self.dk)
         o = ws.get("attn.o", (T, qn), ctx.dtype)
         self.attend(ctx, q, o, cache.kv_pages, table)
+        if self.gate == "head":
+            ops.gate_heads(o, gate, self.nq, self.d)
+        elif self.gate:
+            ops.gate_heads(o, gate, qn, 1)
         if out is None:
             out = ws.get("attn.y", (T, self.hidden), ctx.dtype)
         return linear.linear(o, self.w_o, out, bias=self.b_o)

@@ -326,7 +326,12 @@ class Block(Part):
 
 
 class Embedding(Part):
-    def forward(self, ctx: StepContext, residual: torch.Tensor) -> None:
+    def cache_need(self) -> Optional[CacheNeed]:
+        """What the cache manager keeps per request for the embedding (a ``PerRequestNeed``), or
+        ``None``.  An embedding with a need gets its :class:`CacheView` as ``cache``."""
+        return None
+
+    def forward(self, ctx: StepContext, residual: torch.Tensor, cache: Optional[CacheView] = None) -> None:
         raise NotImplementedError
 
 

@@ -87,7 +87,8 @@ class HyperNorm(Norm):
     ``bias_tensor`` (None: no bias), ``center`` (default True: layer norm - the mean is taken off and
     the variance is the mean of the squared deviations; False: RMS norm), ``connection`` (the prefix
     of the ``in``, ``out`` and ``mix`` tensors below the layer's; None: the norm reads the plain sum
-    of the streams and no branch leaves through it - the model's last norm)."""
+    of the streams and no branch leaves through it - the model's last norm; ``"identity"``: no
+    tensors, every weight is one - with one stream the plain pre-norm residual ``x <- x + y``)."""
 
     graph_capturable = True
 
@@ -101,7 +102,10 @@ class HyperNorm(Norm):
         self.weight_name = self.name(p["tensor"])
         self.bias_name = self.name(p["bias_tensor"]) if p.get("bias_tensor") else None
         conn = p.get("connection")
-        self.conn = {k: self.name(f"{conn}.{k}") for k in ("in", "out", "mix")} if conn else None
+        self.identity = conn == "identity"
+        if self.identity and self.streams != 1:
+            raise ValueError("connection weights of one are the plain residual: they need streams = 1")
+        self.conn = {k: self.name(f"{conn}.{k}") for k in ("in", "out", "mix")} if conn and not self.identity else None
         self.weight = self.bias = self.w_in = self.w_out = self.w_mix = None
 
     def tensor_specs(self) -> List[TensorSpec]:
@@ -121,13 +125,16 @@ class HyperNorm(Norm):
         self.bias = tensors[self.bias_name] if self.bias_name else None
         if self.conn:
             self.w_in, self.w_out, self.w_mix = (tensors[self.conn[k]] for k in ("in", "out", "mix"))
+        elif self.identity:
+            ones = torch.ones(1, dtype=torch.float32, device=self.weight.device)
+            self.w_in, self.w_out, self.w_mix = ones, ones, ones.view(1, 1)
 
     def libraries(self, dtype) -> List[str]:
         return ["rowwise"]
 
     def pending(self, y: torch.Tensor) -> PendingBranch:
         """``y`` (this norm's sublayer's output) with the weights it joins the streams by."""
-        if not self.conn:
+        if not self.conn and not self.identity:
             raise ValueError("a norm without connection weights has no sublayer whose output could leave through it")
         return PendingBranch(y, self.w_mix, self.w_out)
 

@@ -132,3 +132,12 @@ def _load_builtin() -> None:
             config_to_dict=lambda cfg: cfg.to_dict(),
         ),
     )
+    from .config import mezapel
+    register_architecture(
+        Architecture(
+            name=mezapel.ARCHITECTURE,
+            read_config=mezapel.MezapelConfig.from_dict,
+            build_plan=mezapel.build_plan,
+            config_to_dict=lambda cfg: cfg.to_dict(),
+        ),
+    )
