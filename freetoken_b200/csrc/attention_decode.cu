@@ -34,6 +34,7 @@ struct DecodeArgs {
   int nq, nkv, P, table_width, window;
   int n_rows, splits, split_keys;
   float scale;
+  ScoreOpts opt;             // chunks, cap, sink (the sink joins the partial of split 0)
 };
 
 constexpr int TILE = 64;    // keys per tile
@@ -61,7 +62,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
   const int split = blockIdx.z;
   const int pos = a.token_pos[tok];
   const int* table = a.block_table + (size_t)a.token_seg[tok] * a.table_width;
-  const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int lo = first_visible(pos, a.window, a.opt.chunk);
   const int k_begin = max(lo, split * a.split_keys) / TILE * TILE;
   const int k_end = min(pos + 1, (split + 1) * a.split_keys);
   const int first_valid = max(lo, split * a.split_keys);
@@ -130,6 +131,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
     for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows g and g+8
   const float scale_log2 = a.scale * 1.4426950408889634f;
+  const float cap = a.opt.softcap;
 
   for (int tile = 0; tile < ntiles; ++tile) {
     const int pre = tile + STAGES - 1;
@@ -164,7 +166,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
         for (int i = 0; i < 4; ++i) {
           const int j = j0 + 8 * n + 2 * t4 + (i & 1);
           const bool ok = j <= pos && j >= first_valid && j < k_end;
-          s[n][i] = ok ? s[n][i] * scale_log2 : -INFINITY;
+          if (cap > 0.f) s[n][i] = ok ? cap_score(s[n][i] * a.scale, cap) * 1.4426950408889634f : -INFINITY;
+          else s[n][i] = ok ? s[n][i] * scale_log2 : -INFINITY;
           if (i < 2) mx0 = fmaxf(mx0, s[n][i]); else mx1 = fmaxf(mx1, s[n][i]);
         }
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
@@ -254,6 +257,10 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
       acc += red_o[(w * 16 + r) * D + c] * f;
     }
     const int head = head0 + r;
+    if (a.opt.sink_mode && split == 0) {
+      // a score without key or value: it enters the denominator once, with the first split
+      acc *= join_sink_log2(m, l, (a.opt.sink_mode == 2 ? a.opt.sink[head] : a.opt.sink_value) * 1.4426950408889634f);
+    }
     if (a.splits == 1) {
       a.out[((size_t)tok * a.nq + head) * D + c] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
     } else {
@@ -319,13 +326,16 @@ extern "C" int ft_attn_decode(const void* q, void* out, float* part_o, float* pa
                               const int* token_seg, const int* block_table, long long page_stride,
                               long long kv_stride, int nq, int nkv, int d, int P, int table_width,
                               int window, int n_rows, int splits, int split_keys, float scale,
+                              int chunk, float softcap, int sink_mode, float sink_value, const float* sink,
                               cudaStream_t stream) {
   if (n_rows <= 0) return FT_OK;
   if (nkv <= 0 || nq % nkv || splits < 1 || split_keys < TILE || split_keys % TILE) return FT_ERR_SHAPE;
   if (splits > 1 && (!part_o || !part_ml)) return FT_ERR_SHAPE;
   DecodeArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, part_o, part_ml,
                (const __nv_bfloat16*)kv, rows, token_pos, token_seg, block_table, page_stride,
-               kv_stride, nq, nkv, P, table_width, window, n_rows, splits, split_keys, scale};
+               kv_stride, nq, nkv, P, table_width, window, n_rows, splits, split_keys, scale,
+               ScoreOpts{chunk, softcap, sink_mode, sink_value, sink}};
+  if (sink_mode == 2 && !sink) return FT_ERR_SHAPE;
   int rc;
   switch (d) {
     case 32: rc = launch_decode<32>(a, stream); break;

@@ -49,6 +49,7 @@ struct DecodeTmaArgs {
   int nq, nkv, P, table_width, window;
   int n_rows, splits, split_keys;
   float scale;
+  ScoreOpts opt;             // chunks, cap, sink (the sink joins the partial of split 0)
   int v_plane = 1;           // which plane of the cache holds the values (0: the keys are the values)
 };
 
@@ -90,7 +91,7 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_const
   const int split = blockIdx.z;
   const int pos = a.token_pos[tok];
   const int* table = a.block_table + (size_t)a.token_seg[tok] * a.table_width;
-  const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int lo = first_visible(pos, a.window, a.opt.chunk);
   const int k_begin = max(lo, split * a.split_keys) / TILE * TILE;
   const int k_end = min(pos + 1, (split + 1) * a.split_keys);
   const int first_valid = max(lo, split * a.split_keys);
@@ -165,6 +166,7 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_const
     for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows g and g+8
   const float scale_log2 = a.scale * 1.4426950408889634f;
+  const float cap = a.opt.softcap;
 
   for (int tile = 0; tile < ntiles; ++tile) {
     const int stage = tile % STAGES;
@@ -212,7 +214,8 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_const
         for (int i = 0; i < 4; ++i) {
           const int j = j0 + 8 * n + 2 * t4 + (i & 1);
           const bool ok = j <= pos && j >= first_valid && j < k_end;
-          s[n][i] = ok ? s[n][i] * scale_log2 : -INFINITY;
+          if (cap > 0.f) s[n][i] = ok ? cap_score(s[n][i] * a.scale, cap) * 1.4426950408889634f : -INFINITY;
+          else s[n][i] = ok ? s[n][i] * scale_log2 : -INFINITY;
           if (i < 2) mx0 = fmaxf(mx0, s[n][i]); else mx1 = fmaxf(mx1, s[n][i]);
         }
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
@@ -305,6 +308,10 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_const
       acc += red_o[(w * 16 + r) * D + c] * f;
     }
     const int head = head0 + r;
+    if (a.opt.sink_mode && split == 0) {
+      // a score without key or value: it enters the denominator once, with the first split
+      acc *= join_sink_log2(m, l, (a.opt.sink_mode == 2 ? a.opt.sink[head] : a.opt.sink_value) * 1.4426950408889634f);
+    }
     if (CLUSTER) {
       xo[r * D + c] = acc;
       if (c == 0) {
@@ -403,7 +410,8 @@ extern "C" int ft_attn_decode_tma(const void* map_kv, const void* q, void* out, 
                                   float* part_ml, const int* rows, const int* token_pos,
                                   const int* token_seg, const int* block_table, int* status, int nq,
                                   int nkv, int d, int P, int table_width, int window, int n_rows,
-                                  int splits, int split_keys, float scale, int v_plane,
+                                  int splits, int split_keys, float scale, int v_plane, int chunk,
+                                  float softcap, int sink_mode, float sink_value, const float* sink,
                                   cudaStream_t stream) {
   if (n_rows <= 0) return FT_OK;
   if (nkv <= 0 || nq % nkv || splits < 1 || split_keys < DT_TILE || split_keys % DT_TILE || P % DT_TILE)
@@ -413,7 +421,8 @@ extern "C" int ft_attn_decode_tma(const void* map_kv, const void* q, void* out, 
   memcpy(&mkv, map_kv, sizeof(mkv));
   DecodeTmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, part_o, part_ml, rows, token_pos,
                   token_seg, block_table, status, nq, nkv, P, table_width, window, n_rows, splits,
-                  split_keys, scale, v_plane ? 1 : 0};
+                  split_keys, scale, ScoreOpts{chunk, softcap, sink_mode, sink_value, sink}, v_plane ? 1 : 0};
+  if (sink_mode == 2 && !sink) return FT_ERR_SHAPE;
   int rc;
   switch (d) {
     case 64: rc = launch_decode_tma<64>(mkv, a, stream); break;

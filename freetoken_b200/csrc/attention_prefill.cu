@@ -8,7 +8,9 @@
 // ldmatrix, products are mma.sync m16n8k16 bf16 with float32 accumulation,
 // the softmax state (max, sum) and the output accumulator are float32, P is
 // rounded to bf16 before P*V.  Causal by absolute position; a window limits how
-// far back a row looks.
+// far back a row looks, a mask in chunks lets a row see its own chunk of positions only;
+// scores may be capped (cap * tanh(s / cap)) and a sink (a score without key or value) may
+// join the softmax's denominator after the last key tile.
 //
 // Reference: tiled extend kernel over cached prefix + fresh keys,
 // python/freetoken/kernel/triton/attention.py:469-758 (tile 128x64, P cast to
@@ -30,6 +32,7 @@ struct PrefillArgs {
   long long page_stride, kv_stride;
   int nq, nkv, P, table_width, window;
   float scale;
+  ScoreOpts opt;
 };
 
 constexpr int QT = 64;      // query rows per CTA
@@ -61,7 +64,7 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(PrefillArgs a) {
   const int pos_first = a.seg_pos0[seg] + q0;   // position of the tile's first row
   const int pos_last = pos_first + rows - 1;
   const int* table = a.block_table + (size_t)seg * a.table_width;
-  const int lo_tile = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
+  const int lo_tile = first_visible(pos_first, a.window, a.opt.chunk);   // rows further down see no earlier key
   const int k_begin = lo_tile / KT * KT;
   const int ntiles = (pos_last - k_begin) / KT + 1;
 
@@ -106,10 +109,11 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(PrefillArgs a) {
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   const float scale_log2 = a.scale * 1.4426950408889634f;
   const int pos_r0 = pos_first + warp * 16 + g, pos_r1 = pos_r0 + 8;   // this lane's two rows
-  const int lo_r0 = a.window > 0 ? pos_r0 - a.window + 1 : 0;
-  const int lo_r1 = a.window > 0 ? pos_r1 - a.window + 1 : 0;
+  const int lo_r0 = first_visible(pos_r0, a.window, a.opt.chunk);
+  const int lo_r1 = first_visible(pos_r1, a.window, a.opt.chunk);
+  const float cap = a.opt.softcap;
   const int warp_pos_hi = pos_first + warp * 16 + 15;                  // last row of the warp
-  const int warp_lo = a.window > 0 ? pos_first + warp * 16 - a.window + 1 : 0;
+  const int warp_lo = first_visible(pos_first + warp * 16, a.window, a.opt.chunk);
 
   for (int tile = 0; tile < ntiles; ++tile) {
     if (tile + 1 < ntiles) load_tile(tile + 1, (tile + 1) % PSTAGES);
@@ -144,7 +148,8 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(PrefillArgs a) {
         for (int i = 0; i < 4; ++i) {
           const int j = j0 + 8 * nt + 2 * t4 + (i & 1);
           const bool ok = i < 2 ? (j <= pos_r0 && j >= lo_r0) : (j <= pos_r1 && j >= lo_r1);
-          s[nt][i] = ok ? s[nt][i] * scale_log2 : -INFINITY;
+          if (cap > 0.f) s[nt][i] = ok ? cap_score(s[nt][i] * a.scale, cap) * 1.4426950408889634f : -INFINITY;
+          else s[nt][i] = ok ? s[nt][i] * scale_log2 : -INFINITY;
           if (i < 2) mx0 = fmaxf(mx0, s[nt][i]); else mx1 = fmaxf(mx1, s[nt][i]);
         }
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
@@ -195,6 +200,14 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(PrefillArgs a) {
   }
   cp_async_wait<0>();
 
+  if (a.opt.sink_mode) {
+    const float sk = (a.opt.sink_mode == 2 ? a.opt.sink[head] : a.opt.sink_value) * 1.4426950408889634f;
+    const float al0 = join_sink_log2(m0, l0, sk), al1 = join_sink_log2(m1, l1, sk);
+#pragma unroll
+    for (int nn = 0; nn < D / 8; ++nn) {
+      o[nn][0] *= al0; o[nn][1] *= al0; o[nn][2] *= al1; o[nn][3] *= al1;
+    }
+  }
   const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
   const int r0 = warp * 16 + g, r1 = r0 + 8;
 #pragma unroll
@@ -234,12 +247,13 @@ extern "C" int ft_attn_prefill(const void* q, void* out, const void* kv, const i
                                const int* tile_q0, const int* seg_q_start, const int* seg_pos0,
                                const int* block_table, long long page_stride, long long kv_stride,
                                int nq, int nkv, int d, int P, int table_width, int window,
-                               int tiles, float scale, cudaStream_t stream) {
+                               int tiles, float scale, int chunk, float softcap, int sink_mode,
+                               float sink_value, const float* sink, cudaStream_t stream) {
   if (tiles <= 0) return FT_OK;
-  if (nkv <= 0 || nq % nkv) return FT_ERR_SHAPE;
+  if (nkv <= 0 || nq % nkv || (sink_mode == 2 && !sink)) return FT_ERR_SHAPE;
   PrefillArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)kv, tile_seg,
                 tile_q0, seg_q_start, seg_pos0, block_table, page_stride, kv_stride, nq, nkv, P,
-                table_width, window, scale};
+                table_width, window, scale, ScoreOpts{chunk, softcap, sink_mode, sink_value, sink}};
   int rc;
   switch (d) {
     case 32: rc = launch_prefill<32>(a, tiles, stream); break;

@@ -43,6 +43,33 @@ __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+
+// What a softmax attention may do to its scores beyond scale and window (every attention
+// kernel takes the same five values): a mask in chunks, a cap, a sink.
+struct ScoreOpts {
+  int chunk;              // > 0: a query sees the keys of its own chunk of this many positions
+  float softcap;          // > 0: score <- softcap * tanh(score / softcap)
+  int sink_mode;          // 0 none, 1 the score sink_value, 2 sink[query head]
+  float sink_value;
+  const float* sink;      // [nq] float32
+};
+// first key position a query at `pos` sees
+__device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
+  int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  if (chunk > 0) lo = max(lo, pos - pos % chunk);
+  return lo;
+}
+__device__ __forceinline__ float cap_score(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+// The sink joins a running softmax state kept in the log2 domain (max m, sum l): returns the
+// factor on the accumulator, updates m and l.  `sink_log2` is the sink's score times log2(e).
+__device__ __forceinline__ float join_sink_log2(float& m, float& l, float sink_log2) {
+  const float mn = fmaxf(m, sink_log2);
+  const float al = (m == -INFINITY) ? 0.f : exp2f(m - mn);
+  l = l * al + exp2f(sink_log2 - mn);
+  m = mn;
+  return al;
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                               cudaStream_t stream, Args... args) {

@@ -1058,8 +1058,9 @@ def attn_decode(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
                 rows: Optional[torch.Tensor], n_rows: int, token_pos: torch.Tensor,
                 token_seg: torch.Tensor, block_table: torch.Tensor, num_heads: int,
                 num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
-                max_kv_len: int, workspace) -> None:
+                max_kv_len: int, workspace, options: Optional[ScoreOptions] = None) -> None:
     """Split-KV tensor-core attention for single-token rows (bfloat16)."""
+    extra = (options or NO_SCORE_OPTIONS).args(num_heads)
     _need(q, "q", torch.bfloat16)
     _need(out, "out", torch.bfloat16)
     _need_pages(kv_pages, torch.bfloat16)
@@ -1089,29 +1090,30 @@ def attn_decode(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
                       head_dim, kv_pages.stride(2), kv_pages.stride(1), kv_pages.stride(0))
         map_kv = _attn_tc_map("kv", (kv_pages.data_ptr(),) + tuple(kv_pages.shape) + tuple(kv_pages.stride()),
                               make_kv)
-        f = _fn("attention_decode_tma", "ft_attn_decode_tma", "p p p p p p p p p p i i i i i i i i i f i")
+        f = _fn("attention_decode_tma", "ft_attn_decode_tma", "p p p p p p p p p p i i i i i i i i i f i i f i f p")
         _check(f(ctypes.cast(map_kv, ctypes.c_void_p), _ptr(q), _ptr(out), _ptr(part_o), _ptr(part_ml),
                  _ptr(rows), _ptr(token_pos), _ptr(token_seg), _ptr(block_table), _ptr(tc_status(q.device)),
                  num_heads, num_kv_heads, head_dim, kv_pages.shape[3], block_table.shape[1],
                  int(window or 0), n_rows, splits, split_keys, float(scale),
-                 1 if kv_pages.stride(0) else 0, _stream()), "attn_decode_tma")
+                 1 if kv_pages.stride(0) else 0, *extra, _stream()), "attn_decode_tma")
         if part_o is not None:
             fm = _fn("attention_decode", "ft_attn_merge", "p p p p i i i i")
             _check(fm(_ptr(part_o), _ptr(part_ml), _ptr(out), _ptr(rows), n_rows, num_heads, head_dim,
                       splits, _stream()), "attn_merge")
         return
-    f = _fn("attention_decode", "ft_attn_decode", "p p p p p p p p p q q i i i i i i i i i f")
+    f = _fn("attention_decode", "ft_attn_decode", "p p p p p p p p p q q i i i i i i i i i f i f i f p")
     _check(f(_ptr(q), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(kv_pages), _ptr(rows),
              _ptr(token_pos), _ptr(token_seg), _ptr(block_table), kv_pages.stride(1),
              kv_pages.stride(0), num_heads, num_kv_heads, head_dim, kv_pages.shape[3],
              block_table.shape[1], int(window or 0), n_rows, splits, split_keys, float(scale),
-             _stream()), "attn_decode")
+             *extra, _stream()), "attn_decode")
 
 
 def attn_prefill(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
                  tile_seg: torch.Tensor, tile_q0: torch.Tensor, seg_q_start: torch.Tensor,
                  seg_pos0: torch.Tensor, block_table: torch.Tensor, num_heads: int,
-                 num_kv_heads: int, head_dim: int, scale: float, window: Optional[int]) -> None:
+                 num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
+                 options: Optional[ScoreOptions] = None) -> None:
     """Tensor-core causal attention for the query tiles (64 tokens) listed in
     ``tile_seg`` / ``tile_q0`` (bfloat16; head sizes of :data:`DECODE_HEAD_DIMS`)."""
     _need(q, "q", torch.bfloat16)
@@ -1122,11 +1124,11 @@ def attn_prefill(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
     for name, t in (("tile_seg", tile_seg), ("tile_q0", tile_q0), ("seg_q_start", seg_q_start),
                     ("seg_pos0", seg_pos0), ("block_table", block_table)):
         _need(t, name, torch.int32)
-    f = _fn("attention_prefill", "ft_attn_prefill", "p p p p p p p p q q i i i i i i i f")
+    f = _fn("attention_prefill", "ft_attn_prefill", "p p p p p p p p q q i i i i i i i f i f i f p")
     _check(f(_ptr(q), _ptr(out), _ptr(kv_pages), _ptr(tile_seg), _ptr(tile_q0), _ptr(seg_q_start),
              _ptr(seg_pos0), _ptr(block_table), kv_pages.stride(1), kv_pages.stride(0), num_heads,
              num_kv_heads, head_dim, kv_pages.shape[3], block_table.shape[1], int(window or 0),
-             tile_seg.numel(), float(scale), _stream()), "attn_prefill")
+             tile_seg.numel(), float(scale), *(options or NO_SCORE_OPTIONS).args(num_heads), _stream()), "attn_prefill")
 
 
 # A step whose prompt portions score at least this many query-key pairs uses the

@@ -102,22 +102,24 @@ class PagedSoftmaxCore:
         longer segments to a prefill kernel; sizes those refuse (and the
         float32 path) go to the generic kernel.  ``kv_pages`` is ``[2 (K, V),
         pages, kv_heads, page, head_dim]``."""
-        if ops.attn_decode_takes(q, self.d) and (self.options is None or self.options.plain()):
+        if ops.attn_decode_takes(q, self.d):
             plan = ctx.plan(self)
             n_dec, n_tiles = plan.host["num_decode_rows"], plan.host["num_prefill_tiles"]
             if n_dec > 0:
                 ops.attn_decode(q, o, kv_pages, plan.tensors.get("decode_rows"), n_dec,
                                 ctx.token_pos, ctx.token_seg, table, self.nq, self.nkv, self.d,
-                                self.scale, self.window, plan.host["max_decode_kv_len"], ctx.workspace)
+                                self.scale, self.window, plan.host["max_decode_kv_len"], ctx.workspace,
+                                options=self.options)
             if n_tiles > 0:
                 tile_seg, tile_q0 = plan.tensors["tile_seg"], plan.tensors["tile_q0"]
                 if (plan.host["prefill_scores"] >= ops.PREFILL_TC_MIN_SCORES
+                        and (self.options is None or self.options.plain())
                         and ops.attn_prefill_tc_takes(q, kv_pages, self.d, self.window)):
                     ops.attn_prefill_tc(q, o, kv_pages, tile_seg, tile_q0, ctx.seg_q_start,
                                         ctx.seg_pos0, table, self.nq, self.nkv, self.d, self.scale)
                     return
                 ops.attn_prefill(q, o, kv_pages, tile_seg, tile_q0, ctx.seg_q_start, ctx.seg_pos0,
-                                 table, self.nq, self.nkv, self.d, self.scale, self.window)
+                                 table, self.nq, self.nkv, self.d, self.scale, self.window, options=self.options)
             return
         ops.attn_paged_simt(q, o, kv_pages, ctx.token_pos, ctx.token_seg, table,
                             self.nq, self.nkv, self.d, self.scale, self.window, options=self.options)

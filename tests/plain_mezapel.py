@@ -242,3 +242,41 @@ def forward(cfg, w, tokens, trace=None):
             trace.append(sum(streams) if isinstance(streams, list) else streams)
     x = sum(streams) if isinstance(streams, list) else streams
     return layer_norm(x, w["final.norm"], w["final.norm.b"], eps) @ w["head"].T
+
+
+def expected_tensors(cfg):
+    """Name -> shape of every tensor a checkpoint of ``cfg`` holds."""
+    W, V = int(cfg["width"]), int(cfg["vocab"])
+    out = {"embed": (V, W)}
+    big = (cfg.get("embedding") or {}).get("bigram")
+    if big:
+        out["bigram"] = (int(big["buckets"]) + 1, W)
+    S = cfg.get("streams")
+    for i, layer in enumerate(cfg["layers"]):
+        m, p = layer["mixer"], f"l{i}."
+        H, G, D, Vd = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
+        subs = [1] + ([2] if layer.get("mlp") else [])
+        for q in subs:
+            out[f"{p}norm{q}"] = (W,)
+            out[f"{p}norm{q}.b"] = (W,)
+            if S:
+                out[f"{p}hc{q}.in"] = (int(S),)
+                out[f"{p}hc{q}.out"] = (int(S),)
+                out[f"{p}hc{q}.mix"] = (int(S), int(S))
+        out[p + "mix.q"], out[p + "mix.k"], out[p + "mix.v"] = (H * D, W), (G * D, W), (G * Vd, W)
+        out[p + "mix.o"] = (W, H * Vd)
+        if layer["type"] == "attention":
+            out[p + "mix.q.norm"], out[p + "mix.k.norm"] = (H * D,), (G * D,)
+            out[p + "mix.g"] = (H, W)
+        else:
+            out[p + "mix.q.norm"], out[p + "mix.k.norm"] = (D,), (D,)
+            out[p + "mix.g"] = (H * Vd, W)
+            out[p + "mix.sink"] = (H,)
+            if m.get("conv"):
+                taps = int(m["conv"])
+                out[p + "mix.q.conv"], out[p + "mix.k.conv"], out[p + "mix.v.conv"] = (H * D, taps), (G * D, taps), (G * Vd, taps)
+        if layer.get("mlp"):
+            ff = int(layer["mlp"]["ff"])
+            out[p + "mlp.gate"], out[p + "mlp.up"], out[p + "mlp.down"] = (ff, W), (ff, W), (W, ff)
+    out["final.norm"], out["final.norm.b"], out["head"] = (W,), (W,), (V, W)
+    return out
