@@ -346,16 +346,23 @@ def test_an_edge_decides(tmp_path, kind, dim, page, size, dtype):
 @pytest.mark.parametrize("kind", ["attention", "attention_2"])
 def test_a_far_key_decides(tmp_path, kind, dtype):
     """One key among hundreds, 300 to 450 positions back inside a chunk of 512 (a window of 500),
-    right before, on and right after a page border and first of all: it alone has a value."""
+    right before, on and right after a page border and first of all: it alone has a value, and the
+    output projection is made twelve times as large, so that a weight of 1/450 on that value moves
+    the logits (a value large enough to do that alone would cost the other tokens' small values
+    their precision in bfloat16: they are differences of products of the rounded input; for the
+    same reason the vocabulary is a quarter of the width here, and in bfloat16 the first 32
+    positions, where few keys share the weight and that rounding is not averaged away, are left to
+    the other tests)."""
     size = 512 if kind == "attention" else 500
-    config = mz.one_layer(edge_layer(kind, 16, 12, size), vocab=40, width=48, streams=2, bigram=None)
+    config = mz.one_layer(edge_layer(kind, 16, 12, size), vocab=12, width=48, streams=2, bigram=None)
     state = mz.random_state(config, 43)
     target, stand_in = 5, 6
-    only_the_target_has_a_value(config, state, target, big=600.0)
+    only_the_target_has_a_value(config, state, target, big=40.0)
+    state["l0.mix.o"] = (state["l0.mix.o"] * 12.0).to(torch.bfloat16).double()
     page, n = 16, 470
     reqs = {}
     for place in (15, 16, 17, 0, 145):
-        toks = [t if t != target else stand_in for t in mz.tokens(70 + place, n, 40)]
+        toks = [t if t != target else stand_in for t in mz.tokens(70 + place, n, 12)]
         toks[place] = target
         reqs[f"t{place}"] = toks
     want = {rid: plain.forward(config, state, t) for rid, t in reqs.items()}
@@ -366,7 +373,10 @@ def test_a_far_key_decides(tmp_path, kind, dtype):
     for cut in ("decode_tail", "portions", "mixed"):
         schedule = CUTS[cut](reqs)
         engine = mz.make_engine(folder, dtype, page, rd.peak_tokens(schedule, page), poison=True)
-        mz.compare(rd.run_engine(engine, reqs, schedule), want, mz.TOL[dtype], f"far key, {kind}, {cut} [{dtype}]")
+        first = 32 if dtype == "bfloat16" else 0
+        got = rd.run_engine(engine, reqs, schedule)
+        mz.compare({rid: g[first:] for rid, g in got.items()}, {rid: w[first:] for rid, w in want.items()}, mz.TOL[dtype],
+                   f"far key, {kind}, {cut} [{dtype}]")
 
 
 # ------------------------------------------------- long prompts at sizes between tiny and real
