@@ -7,7 +7,8 @@ engine is single-GPU: for ``--gpus N`` with N > 1 it says so and exits with 2.
 ``--design fazinex`` runs, instead of the default workload, the Fazinex decoder beside the
 MiniMax-M3 decoder at equal size (freetoken_b200/design_bench.py); ``--design tonapel`` does the
 same for the Tonapel decoder (freetoken_b200/tonapel_bench.py), ``--design nirelix`` runs the Nirelix
-decoder beside the Tonapel decoder at equal size (freetoken_b200/nirelix_bench.py).
+decoder beside the Tonapel decoder at equal size (freetoken_b200/nirelix_bench.py), ``--design mezapel``
+the Mezapel decoder beside the MiniMax-M3 decoder at equal size (freetoken_b200/mezapel_bench.py).
 """
 import os
 import sys

@@ -235,7 +235,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--equivalence", action="store_true",
                    help="instead of timing: the same random model (--layers, default 2) in float32 and in "
                         "bfloat16 on one 512-token prompt and 8 decoded tokens; prints how far the logits differ")
-    p.add_argument("--design", default=None, choices=["fazinex", "tonapel", "nirelix"],
+    p.add_argument("--design", default=None, choices=["fazinex", "tonapel", "nirelix", "mezapel"],
                    help="instead of the default workload: this design beside the MiniMax-M3 decoder at "
                         "equal size (prefill and decode steps, and the design's kernels against their rooflines)")
     p.add_argument("--sizes", default="w2048,w4096", help="with --design: which layer sizes to run")
@@ -265,6 +265,9 @@ def main(argv: Optional[List[str]] = None) -> int:
         if a.design == "nirelix":
             from . import nirelix_bench
             return nirelix_bench.main(a)
+        if a.design == "mezapel":
+            from . import mezapel_bench
+            return mezapel_bench.main(a)
         return (tonapel_bench if a.design == "tonapel" else design_bench).main(a)
 
     from .csrc import ops

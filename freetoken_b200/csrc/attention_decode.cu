@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
         for (int i = 0; i < 4; ++i) {
           const int j = j0 + 8 * n + 2 * t4 + (i & 1);
           const bool ok = j <= pos && j >= first_valid && j < k_end;
-          if (cap > 0.f) s[n][i] = ok ? cap_score(s[n][i] * a.scale, cap) * 1.4426950408889634f : -INFINITY;
+          if (cap > 0.f) s[n][i] = ok ? cap_score_fast(s[n][i] * a.scale, cap) * 1.4426950408889634f : -INFINITY;
           else s[n][i] = ok ? s[n][i] * scale_log2 : -INFINITY;
           if (i < 2) mx0 = fmaxf(mx0, s[n][i]); else mx1 = fmaxf(mx1, s[n][i]);
         }

@@ -148,7 +148,7 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_kernel(PrefillArgs a) {
         for (int i = 0; i < 4; ++i) {
           const int j = j0 + 8 * nt + 2 * t4 + (i & 1);
           const bool ok = i < 2 ? (j <= pos_r0 && j >= lo_r0) : (j <= pos_r1 && j >= lo_r1);
-          if (cap > 0.f) s[nt][i] = ok ? cap_score(s[nt][i] * a.scale, cap) * 1.4426950408889634f : -INFINITY;
+          if (cap > 0.f) s[nt][i] = ok ? cap_score_fast(s[nt][i] * a.scale, cap) * 1.4426950408889634f : -INFINITY;
           else s[nt][i] = ok ? s[nt][i] * scale_log2 : -INFINITY;
           if (i < 2) mx0 = fmaxf(mx0, s[nt][i]); else mx1 = fmaxf(mx1, s[nt][i]);
         }

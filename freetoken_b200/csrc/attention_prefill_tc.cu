@@ -3,7 +3,8 @@
 //
 // A CTA owns 128 query tokens of one segment and one query head and walks the
 // key tiles (64 keys, one TMA box per 64 head dims, through the block table)
-// from key 0 to the tile's diagonal:
+// from the first key its first row sees (key 0, or the start of a window or of a
+// chunk of positions) to the tile's diagonal:
 //
 //   S[128 q, 64 keys]  = Q K^T      tcgen05.mma, Q and K both K-major from shared
 //                                    memory, accumulator in TMEM
@@ -22,6 +23,10 @@
 // S has two TMEM buffers: the S product of tile j+1 is issued before the O
 // product of tile j, so it runs under the softmax of tile j.  Two CTAs fit an SM
 // (96 KB of shared memory and 256 TMEM columns each at head size 128).
+//
+// Options: a window or a mask in chunks (rows mask the keys before their own first
+// visible one), scores capped by cap * tanh(s / cap), and a sink - a score without key
+// or value that joins a row's denominator after its last tile.
 //
 // Every mbarrier wait is bounded (about two seconds): on expiry the CTA writes
 // a code into `status`, stops issuing work, frees its TMEM and returns.
@@ -52,6 +57,9 @@ struct PrefillTcArgs {
   int* status;
   int nq, nkv, P, table_width;
   float scale_log2;          // sm_scale * log2(e)
+  float scale;               // sm_scale
+  int window;                // > 0: a row sees its own key and the window - 1 before it
+  ScoreOpts opt;             // chunks, cap, sink
   int v_plane = 1;           // which plane of the cache holds the values (0: the keys are the values)
 };
 
@@ -94,9 +102,12 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
   const int rows = min(TOK, n - q0);                  // tokens this CTA really has
   const int tok0 = seg_begin + q0;
   const int pos_first = a.seg_pos0[seg] + q0;
-  const int ntiles = (pos_first + rows - 1) / AK + 1;
+  // tile j of this CTA holds keys (tile0 + j) * AK ..: tile0 is the tile of the first key the
+  // first row sees (later rows see no earlier one)
+  const int tile0 = first_visible(pos_first, a.window, a.opt.chunk) / AK;
+  const int ntiles = (pos_first + rows - 1) / AK + 1 - tile0;
   // keys of the last tile past the segment's last token: whatever the page held before
-  const int stale_from = pos_first + rows - (ntiles - 1) * AK;      // first such key row, AK if none
+  const int stale_from = pos_first + rows - (tile0 + ntiles - 1) * AK;      // first such key row, AK if none
 
   if (threadIdx.x == 0) {
     gave_up = 0;
@@ -141,7 +152,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
             gave_up = 1;
             break;
           }
-          const int key0 = j * AK;
+          const int key0 = (tile0 + j) * AK;
           const int page = table[key0 / a.P], off = key0 % a.P;
           mbar_expect_tx(&k_full[s], K_BYTES);
 #pragma unroll
@@ -156,7 +167,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
             gave_up = 1;
             break;
           }
-          const int key0 = i * AK;
+          const int key0 = (tile0 + i) * AK;
           const int page = table[key0 / a.P], off = key0 % a.P;
           mbar_expect_tx(&v_full[s], K_BYTES);
 #pragma unroll
@@ -265,6 +276,9 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
     const unsigned lane_bits = (unsigned)lane_base << 16;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
+    const int my_lo = first_visible(my_pos, a.window, a.opt.chunk);
+    const int last_lo = first_visible(pos_first + rows - 1, a.window, a.opt.chunk);   // no row's first key lies later
+    const float cap = a.opt.softcap;
     for (int j = 0; j < ntiles; ++j) {
       const unsigned tmem_sj = tmem_s + (unsigned)((j & 1) * AK) + lane_bits;
       ok = mbar_wait(&s_full[j & 1], ((unsigned)j >> 1) & 1u, &gave_up);
@@ -276,7 +290,15 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
       tc_ld32(tmem_sj, lo);
       tc_ld32(tmem_sj + 32, hi);
       tc_ld_wait();
-      const int key0 = j * AK;
+      const int key0 = (tile0 + j) * AK;
+      if (key0 < last_lo) {
+        // a tile some row's window or chunk starts in (or behind): keys before the row's first one do not count
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          if (key0 + c < my_lo) lo[c] = 0xff800000u;
+          if (key0 + 32 + c < my_lo) hi[c] = 0xff800000u;
+        }
+      }
       if (key0 + AK - 1 > pos_first) {
         // a tile on the diagonal: keys after the row's own position do not count
 #pragma unroll
@@ -296,7 +318,9 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
       // that exp2(s - max) stays far inside float32 and bfloat16 range, and the
       // round trip of O through registers is saved.  The softmax is the same
       // function of the scores whichever offset is subtracted.
-      const float cand = raw * a.scale_log2;
+      // (the cap grows with the score, so the largest score gives the largest capped one)
+      const float cand = cap > 0.f ? (raw == -INFINITY ? raw : cap_score_fast(raw * a.scale, cap) * 1.4426950408889634f)
+                                   : raw * a.scale_log2;
       const float m_new = cand > m + 8.f ? cand : m;
       if (j > 0 && __any_sync(0xffffffffu, m_new != m)) {
         // O must be at rest: the previous tile's O product done (the one before it
@@ -306,7 +330,7 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
         tc_fence_after();
-        const float alpha = fast_exp2(m - m_new);
+        const float alpha = (m == -INFINITY) ? 0.f : fast_exp2(m - m_new);     // nothing seen yet: O holds 0
 #pragma unroll 1
         for (int c0 = 0; c0 < D; c0 += 32) {
           unsigned o[32];
@@ -322,15 +346,26 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
       m = m_new;
       // P = exp2(s * scale - max), summed in float32, rounded to bfloat16 and written
       // over S: column c of the buffer holds keys 2c and 2c+1
-      const float neg_m = -m_new;
+      const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;       // a row that has seen no key yet: every P is 0
       // packed pairs: one fma.rn.f32x2 / add.f32x2 does two elements
       const float2 sc2 = make_float2(a.scale_log2, a.scale_log2), nm2 = make_float2(neg_m, neg_m);
       float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       unsigned pk[32];
+      if (cap > 0.f) {
+        // capped scores: s <- cap * tanh(s * scale / cap), in place, already in the log2 domain
+        const float l2 = 1.4426950408889634f;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float x = __uint_as_float(lo[c]), y = __uint_as_float(hi[c]);
+          lo[c] = __float_as_uint(x == -INFINITY ? x : cap_score_fast(x * a.scale, cap) * l2);
+          hi[c] = __float_as_uint(y == -INFINITY ? y : cap_score_fast(y * a.scale, cap) * l2);
+        }
+      }
+      const float2 sc2c = cap > 0.f ? make_float2(1.f, 1.f) : sc2;
 #pragma unroll
       for (int c = 0; c < 16; ++c) {
-        const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(lo[2 * c]), __uint_as_float(lo[2 * c + 1])), sc2, nm2);
-        const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(hi[2 * c]), __uint_as_float(hi[2 * c + 1])), sc2, nm2);
+        const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(lo[2 * c]), __uint_as_float(lo[2 * c + 1])), sc2c, nm2);
+        const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(hi[2 * c]), __uint_as_float(hi[2 * c + 1])), sc2c, nm2);
         const float2 p01 = make_float2(fast_exp2(x0.x), fast_exp2(x0.y));
         const float2 p23 = make_float2(fast_exp2(x1.x), fast_exp2(x1.y));
         sum2[c & 3] = __fadd2_rn(sum2[c & 3], __fadd2_rn(p01, p23));
@@ -367,7 +402,13 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(const __grid_co
     }
     if (ok) {
       tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      float tail = 1.f;
+      if (a.opt.sink_mode) {
+        // the sink joins the denominator once, after the last key
+        const int sink_head = min(my_head, a.nq - 1);
+        tail = join_sink_log2(m, l, (a.opt.sink_mode == 2 ? a.opt.sink[sink_head] : a.opt.sink_value) * 1.4426950408889634f);
+      }
+      const float inv = l > 0.f ? tail / l : 0.f;
       __nv_bfloat16* orow = a.out + ((size_t)(tok0 + my_tok) * a.nq + my_head) * D;
 #pragma unroll 1
       for (int c0 = 0; c0 < D; c0 += 32) {
@@ -483,7 +524,7 @@ int ft_attn_tc_kv_map(void* out, const void* base, long long pages, long long nk
   return FT_OK;
 }
 
-// bfloat16; head_dim 64 or 128; page size a multiple of 64; no window.
+// bfloat16; head_dim 64 or 128; page size a multiple of 64; window <= 0: none.
 // tile_seg / tile_q0 list the query tiles (64 tokens) of the segments to
 // process.  With an even number of query heads per KV head a CTA takes one tile
 // and two heads (`map_q2`: boxes of 64 rows); otherwise an even tile with its
@@ -491,16 +532,18 @@ int ft_attn_tc_kv_map(void* out, const void* base, long long pages, long long nk
 int ft_attn_prefill_tc(const void* map_q, const void* map_q2, const void* map_kv, void* out, const int* tile_seg,
                        const int* tile_q0, const int* seg_q_start, const int* seg_pos0,
                        const int* block_table, int* status, int nq, int nkv, int d, int P,
-                       int table_width, int tiles, float scale, int v_plane, cudaStream_t stream) {
+                       int table_width, int tiles, float scale, int v_plane, int window, int chunk, float softcap,
+                       int sink_mode, float sink_value, const float* sink, cudaStream_t stream) {
   if (tiles <= 0) return FT_OK;
-  if (nkv <= 0 || nq % nkv || P % AK) return FT_ERR_SHAPE;
+  if (nkv <= 0 || nq % nkv || P % AK || (sink_mode == 2 && !sink)) return FT_ERR_SHAPE;
   CUtensorMap mq, mq2, mkv;
   memcpy(&mq, map_q, sizeof(mq));
   memcpy(&mq2, map_q2, sizeof(mq2));
   memcpy(&mkv, map_kv, sizeof(mkv));
   const bool pair = ((nq / nkv) % 2) == 0;
   PrefillTcArgs a{(__nv_bfloat16*)out, tile_seg, tile_q0, seg_q_start, seg_pos0, block_table, status,
-                  nq, nkv, P, table_width, scale * 1.4426950408889634f, v_plane ? 1 : 0};
+                  nq, nkv, P, table_width, scale * 1.4426950408889634f, scale, window,
+                  ScoreOpts{chunk, softcap, sink_mode, sink_value, sink}, v_plane ? 1 : 0};
   int rc;
   switch (d) {
     case 64:

@@ -60,6 +60,15 @@ __device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
   return lo;
 }
 __device__ __forceinline__ float cap_score(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+// The same for the tensor-core kernels' softmax threads, which are short of issue slots: tanh(x) =
+// 1 - 2 / (1 + e^(2x)) from one ex2.approx and one fast division (absolute error of the tanh about
+// 1e-6, far below what the bfloat16 operands of a score leave; no NaN at either end: e^(2x) = inf
+// gives 1, e^(2x) = 0 gives -1).
+__device__ __forceinline__ float cap_score_fast(float s, float cap) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(s * (2.885390081777927f / cap)));
+  return cap - __fdividef(2.f * cap, 1.f + e);
+}
 // The sink joins a running softmax state kept in the log2 domain (max m, sum l): returns the
 // factor on the accumulator, updates m and l.  `sink_log2` is the sink's score times log2(e).
 __device__ __forceinline__ float join_sink_log2(float& m, float& l, float sink_log2) {

@@ -1155,9 +1155,9 @@ def _attn_tc_map(kind: str, key: tuple, make) -> ctypes.Array:
 
 def attn_prefill_tc_takes(q: torch.Tensor, kv_pages: torch.Tensor, head_dim: int,
                           window: Optional[int]) -> bool:
-    """bfloat16, head size 64 or 128, pages of a multiple of 64 tokens, all keys visible."""
+    """bfloat16, head size 64 or 128, pages of a multiple of 64 tokens (any window)."""
     return (q.dtype == torch.bfloat16 and kv_pages.dtype == torch.bfloat16 and head_dim in (64, 128)
-            and window is None and kv_pages.shape[3] % 64 == 0 and q.stride(1) == 1
+            and kv_pages.shape[3] % 64 == 0 and q.stride(1) == 1
             and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and kv_pages.data_ptr() % 16 == 0
             and kv_pages.stride(4) == 1 and kv_pages.stride(3) == head_dim)
 
@@ -1165,7 +1165,8 @@ def attn_prefill_tc_takes(q: torch.Tensor, kv_pages: torch.Tensor, head_dim: int
 def attn_prefill_tc(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
                     tile_seg: torch.Tensor, tile_q0: torch.Tensor, seg_q_start: torch.Tensor,
                     seg_pos0: torch.Tensor, block_table: torch.Tensor, num_heads: int,
-                    num_kv_heads: int, head_dim: int, scale: float) -> None:
+                    num_kv_heads: int, head_dim: int, scale: float, window: Optional[int] = None,
+                    options: Optional[ScoreOptions] = None) -> None:
     """Causal attention on tcgen05/TMEM with K and V pages fetched by TMA, for the
     query tiles (64 tokens; the kernel pairs them) in ``tile_seg`` / ``tile_q0``."""
     _need(q, "q", torch.bfloat16)
@@ -1198,12 +1199,13 @@ def attn_prefill_tc(q: torch.Tensor, out: torch.Tensor, kv_pages: torch.Tensor,
     map_kv = _attn_tc_map("kv", (kv_pages.data_ptr(),) + tuple(kv_pages.shape) + tuple(kv_pages.stride()),
                           make_kv)
     status = tc_status(q.device)
-    f = _fn("attention_prefill_tc", "ft_attn_prefill_tc", "p p p p p p p p p p i i i i i i f i")
+    f = _fn("attention_prefill_tc", "ft_attn_prefill_tc", "p p p p p p p p p p i i i i i i f i i i f i f p")
     _check(f(ctypes.cast(map_q, ctypes.c_void_p), ctypes.cast(map_q2, ctypes.c_void_p),
              ctypes.cast(map_kv, ctypes.c_void_p), _ptr(out),
              _ptr(tile_seg), _ptr(tile_q0), _ptr(seg_q_start), _ptr(seg_pos0), _ptr(block_table),
              _ptr(status), num_heads, num_kv_heads, head_dim, kv_pages.shape[3], block_table.shape[1],
-             tile_seg.numel(), float(scale), 1 if kv_pages.stride(0) else 0, _stream()), "attn_prefill_tc")
+             tile_seg.numel(), float(scale), 1 if kv_pages.stride(0) else 0, int(window or 0),
+             *(options or NO_SCORE_OPTIONS).args(num_heads), _stream()), "attn_prefill_tc")
 
 
 # ---------------------------------------------------------------- router

@@ -736,11 +736,47 @@ __global__ void __launch_bounds__(256) embed_pair_kernel(EmbedPairArgs a) {
     }
   }
   float* out = a.residual + (size_t)t * a.H * a.copies;
+  // four elements a step where the rows allow it (8-byte loads of bfloat16, 16-byte stores)
+  if ((a.H & 3) == 0 && (((uintptr_t)a.table | (uintptr_t)a.pair_table | (uintptr_t)a.residual) & 15) == 0 &&
+      (a.H * sizeof(WT)) % 16 == 0) {
+    for (int i = threadIdx.x; i < (a.H >> 2); i += blockDim.x) {
+      float4 v = load4f(row + 4 * i);
+      v.x *= a.scale; v.y *= a.scale; v.z *= a.scale; v.w *= a.scale;
+      if (pair) {
+        const float4 b = load4f(pair + 4 * i);
+        v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+      }
+      for (int c = 0; c < a.copies; ++c) *reinterpret_cast<float4*>(out + (size_t)c * a.H + 4 * i) = v;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < a.H; i += blockDim.x) {
     float v = to_float(row[i]) * a.scale;
     if (pair) v += to_float(pair[i]);
     for (int c = 0; c < a.copies; ++c) out[(size_t)c * a.H + i] = v;
   }
+}
+
+// o[t, i] *= sigmoid(z[t, i]): a gate per value, 16-byte pieces of eight bfloat16 values
+__global__ void __launch_bounds__(256)
+gate_values_bf16x8_kernel(__nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ z, long long ldz, int n8,
+                          long long pieces) {
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= pieces) return;
+  const long long t = i / n8;
+  const int c = (int)(i - t * n8);
+  uint4* p = reinterpret_cast<uint4*>(o) + i;
+  uint4 raw = *p;
+  const uint4 zr = *reinterpret_cast<const uint4*>(z + t * ldz + 8 * c);
+  __nv_bfloat162* v = reinterpret_cast<__nv_bfloat162*>(&raw);
+  const __nv_bfloat162* g = reinterpret_cast<const __nv_bfloat162*>(&zr);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(v[j]), zz = __bfloat1622float2(g[j]);
+    v[j] = __floats2bfloat162_rn(f.x / (1.f + expf(-zz.x)), f.y / (1.f + expf(-zz.y)));
+  }
+  *p = raw;
 }
 
 }  // namespace ft
@@ -807,6 +843,14 @@ int ft_key_store(const void* src, void* q_out, void* pages, const float* k_weigh
 int ft_gate_heads(void* o, const void* z, long long ldz, int heads, int d, int dtype, int T, cudaStream_t stream) {
   if (T <= 0) return FT_OK;
   const long long n = (long long)T * heads * d;
+  if (dtype == FT_DTYPE_BF16 && d == 1 && !(heads & 7) && !(ldz & 7) && !((uintptr_t)o & 15) && !((uintptr_t)z & 15)) {
+    // a gate per value: both rows in 16-byte pieces
+    const long long pieces = n >> 3;
+    launch_pdl(gate_values_bf16x8_kernel, dim3((unsigned)((pieces + 255) / 256)), dim3(256), 0, stream,
+               (__nv_bfloat16*)o, (const __nv_bfloat16*)z, ldz, heads >> 3, pieces);
+    FT_LAUNCH_CHECK();
+    return FT_OK;
+  }
   if (dtype == FT_DTYPE_BF16 && !(d & 7) && !((uintptr_t)o & 15)) {
     const long long pieces = n >> 3;
     launch_pdl(gate_heads_kernel<__nv_bfloat16, 8>, dim3((unsigned)((pieces + 255) / 256)), dim3(256), 0, stream,

@@ -113,10 +113,10 @@ class PagedSoftmaxCore:
             if n_tiles > 0:
                 tile_seg, tile_q0 = plan.tensors["tile_seg"], plan.tensors["tile_q0"]
                 if (plan.host["prefill_scores"] >= ops.PREFILL_TC_MIN_SCORES
-                        and (self.options is None or self.options.plain())
                         and ops.attn_prefill_tc_takes(q, kv_pages, self.d, self.window)):
                     ops.attn_prefill_tc(q, o, kv_pages, tile_seg, tile_q0, ctx.seg_q_start,
-                                        ctx.seg_pos0, table, self.nq, self.nkv, self.d, self.scale)
+                                        ctx.seg_pos0, table, self.nq, self.nkv, self.d, self.scale, self.window,
+                                        options=self.options)
                     return
                 ops.attn_prefill(q, o, kv_pages, tile_seg, tile_q0, ctx.seg_q_start, ctx.seg_pos0,
                                  table, self.nq, self.nkv, self.d, self.scale, self.window, options=self.options)

@@ -142,6 +142,10 @@ OPTION_CASES = [
     (16, 1, 64, 16, [(500, 1), (40, 65)], None, 200, 4.0, "learned"),
     (4, 4, 128, 128, [(1000, 3), (0, 2), (1279, 1), (1280, 1)], None, 640, 0.0, "learned"),
     (2, 1, 96, 32, [(90, 40)], 33, None, 30.0, "learned"),                                   # a head size only the generic kernel takes
+    (4, 2, 128, 64, [(0, 300), (700, 130), (5, 1)], 100, None, 0.0, "learned"),             # a window that starts inside key tiles
+    (3, 1, 64, 64, [(30, 260), (0, 2)], None, 96, 6.0, "zero"),                             # chunks across tiles; three heads a key head
+    (2, 2, 128, 128, [(250, 200)], 64, None, 0.0, None),                                     # a window of one tile, nothing else
+    (4, 1, 64, 64, [(1000, 150), (64, 64)], None, 512, 25.0, "learned"),
 ]
 
 
@@ -195,6 +199,14 @@ def test_attention_options_tensor_core_kernels(nq, nkv, d, P, lens, window, chun
         ops.attn_prefill(qd, out, kvd, dev([t[0] for t in tiles]), dev([t[1] for t in tiles]), dev(starts),
                          dev([p for p, _ in lens]), tabled, nq, nkv, d, scale, window, options=opts)
         close(out[many], want[many], "bfloat16", "prefill")
+        if d in (64, 128) and P % 64 == 0:
+            # the tcgen05 kernel: tiles of 128 rows, K and V by TMA
+            out = torch.zeros_like(qd)
+            assert ops.attn_prefill_tc_takes(qd, kvd, d, window)
+            ops.attn_prefill_tc(qd, out, kvd, dev([t[0] for t in tiles]), dev([t[1] for t in tiles]), dev(starts),
+                                dev([p for p, _ in lens]), tabled, nq, nkv, d, scale, window, options=opts)
+            ops.check_tc_status(DEV)
+            close(out[many], want[many], "bfloat16", "prefill on tcgen05")
     if single:
         longest = max(pos[r] for r in single) + 1
         for tma, cluster, reach in ((True, True, longest), (True, False, longest), (False, True, longest),
