@@ -757,7 +757,8 @@ __global__ void __launch_bounds__(256) embed_pair_kernel(EmbedPairArgs a) {
   }
 }
 
-// o[t, i] *= sigmoid(z[t, i]): a gate per value, 16-byte pieces of eight bfloat16 values
+// o[t, i] *= sigmoid(z[t, i]): a gate per value, 16-byte pieces of eight bfloat16 values (the sigmoid from the
+// fast exponential and division: float32 arithmetic whose error lies far below the bfloat16 result's rounding)
 __global__ void __launch_bounds__(256)
 gate_values_bf16x8_kernel(__nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ z, long long ldz, int n8,
                           long long pieces) {
@@ -774,7 +775,7 @@ gate_values_bf16x8_kernel(__nv_bfloat16* __restrict__ o, const __nv_bfloat16* __
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const float2 f = __bfloat1622float2(v[j]), zz = __bfloat1622float2(g[j]);
-    v[j] = __floats2bfloat162_rn(f.x / (1.f + expf(-zz.x)), f.y / (1.f + expf(-zz.y)));
+    v[j] = __floats2bfloat162_rn(__fdividef(f.x, 1.f + __expf(-zz.x)), __fdividef(f.y, 1.f + __expf(-zz.y)));
   }
   *p = raw;
 }

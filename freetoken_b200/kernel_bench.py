@@ -190,6 +190,23 @@ def attn_prefill(sets: int = 1, tc: bool = False, T: int = 2048):
     return run, 0, 4.0 * NQ * D * (T * (T + 1) / 2), "tensor"
 
 
+def attn_prefill_tc_window():
+    """One 8,192-token prompt, 48 heads of 128, a window of 1,024 keys, capped scores and a learned sink per
+    head on tcgen05/TMEM (the work counted is the query-key pairs the window leaves)."""
+    T, window = 8192, 1024
+    kv, table = _kv(1, T, 1)
+    q = torch.randn(T, NQ * D, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty_like(q)
+    i32 = lambda xs: torch.tensor(xs, dtype=torch.int32, device=DEV)
+    tiles = list(range(0, T, 64))
+    lists = (i32([0] * len(tiles)), i32(tiles), i32([0, T]), i32([0]))
+    options = ops.ScoreOptions(softcap=30.0, sink=torch.randn(NQ, device=DEV))
+
+    def run(i):
+        ops.attn_prefill_tc(q, out, kv[0], *lists, table, NQ, NKV, D, D ** -0.5, window, options=options)
+    return run, 0, 4.0 * NQ * D * sum(min(i + 1, window) for i in range(T)), "tensor"
+
+
 def attn_prefill_tc():
     """One 2,048-token prompt, 48 heads of 128: tcgen05/TMEM with TMA-fed pages."""
     return attn_prefill(tc=True)
@@ -295,6 +312,7 @@ KERNELS: Dict[str, Callable[[], Tuple[Callable[[int], None], int, float, str]]] 
     "attn_decode": attn_decode, "attn_decode_one_plane": attn_decode_one_plane, "key_store": key_store,
     "attn_decode_32k": attn_decode_32k, "attn_prefill": attn_prefill, "attn_prefill_tc": attn_prefill_tc,
     "attn_prefill_8k": attn_prefill_8k, "attn_prefill_tc_8k": attn_prefill_tc_8k, "router": router,
+    "attn_prefill_tc_window": attn_prefill_tc_window,
     "peak_copy": peak_copy, "peak_read": peak_read, "peak_gemm": peak_gemm,
     "attn_decode_flashinfer": attn_decode_flashinfer, "attn_decode_32k_flashinfer": attn_decode_32k_flashinfer,
     "attn_prefill_flashinfer": attn_prefill_flashinfer, "attn_prefill_8k_flashinfer": attn_prefill_8k_flashinfer,
