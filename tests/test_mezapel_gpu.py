@@ -360,11 +360,12 @@ def test_a_far_key_decides(tmp_path, kind, dtype):
     """One key among hundreds, 300 to 450 positions back inside a chunk of 512 (a window of 500),
     right before, on and right after a page border and first of all: it alone has a value, and the
     output projection is made twelve times as large, so that a weight of 1/450 on that value moves
-    the logits (a value large enough to do that alone would cost the other tokens' small values
-    their precision in bfloat16: they are differences of products of the rounded input; for the
-    same reason the vocabulary is a quarter of the width here, and in bfloat16 the first 160
-    positions, where few keys share the weight and that rounding is not averaged away, are left to
-    the other tests: the positions that ask 300 and more keys back are all compared)."""
+    the logits.  In bfloat16 the other tokens' small values are differences of products of the
+    rounded input and come out up to 0.08 off whatever computes them (which is also why the
+    vocabulary is a quarter of the width here, and why the value is not simply made larger); with
+    the softmax whose sink is only 1, where a token's own value keeps much of the weight, that shows
+    as an error of up to 0.18 at some tokens, so the bound there is 0.2 - a fifth of what losing the
+    far key costs."""
     size = 512 if kind == "attention" else 500
     config = mz.one_layer(edge_layer(kind, 16, 12, size), vocab=12, width=48, streams=2, bigram=None)
     state = mz.random_state(config, 43)
@@ -380,15 +381,13 @@ def test_a_far_key_decides(tmp_path, kind, dtype):
     want = {rid: plain.forward(config, state, t) for rid, t in reqs.items()}
     other = list(reqs["t16"])
     other[16] = stand_in
-    assert float(mz.position_errors(plain.forward(config, state, other)[-1:], want["t16"][-1:])) > 0.2
+    tol = 0.2 if (kind, dtype) == ("attention", "bfloat16") else mz.TOL[dtype]
+    assert float(mz.position_errors(plain.forward(config, state, other)[-1:], want["t16"][-1:])) > max(0.2, 4 * tol)
     folder = mz.write(str(tmp_path / "m"), config, state)
     for cut in ("decode_tail", "portions", "mixed"):
         schedule = CUTS[cut](reqs)
         engine = mz.make_engine(folder, dtype, page, rd.peak_tokens(schedule, page), poison=True)
-        first = 160 if dtype == "bfloat16" else 0
-        got = rd.run_engine(engine, reqs, schedule)
-        mz.compare({rid: g[first:] for rid, g in got.items()}, {rid: w[first:] for rid, w in want.items()}, mz.TOL[dtype],
-                   f"far key, {kind}, {cut} [{dtype}]")
+        mz.compare(rd.run_engine(engine, reqs, schedule), want, tol, f"far key, {kind}, {cut} [{dtype}]")
 
 
 # ------------------------------------------------- long prompts at sizes between tiny and real
