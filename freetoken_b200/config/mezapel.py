@@ -114,8 +114,8 @@ def _read_mixer(kind: str, m: Any, where: str) -> MezapelMixer:
         _positive(where + "rot.scaling.", factor=values["factor"], original=values["original"])
         if rule == "yarn":
             _positive(where + "rot.scaling.", fast=values["fast"], slow=values["slow"])
-        elif values["high"] == values["low"]:
-            raise ConfigError(f"config.json: '{where}rot.scaling.high' must differ from 'low'")
+        else:
+            _positive(where + "rot.scaling.", low=values["low"], high=values["high"])
         scaling = tuple(sorted(values.items(), key=lambda kv: kv[0]))
     mask = int((m.get("mask") or {}).get("size") or 0)
     if mask < 0:

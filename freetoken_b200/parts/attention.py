@@ -320,7 +320,11 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
                           activation=False)
             qkv = mixed
         elif self.taps == 1:
-            raise ValueError("a convolution of one tap is a factor per channel: fold it into the projection")
+            # one tap: a factor per channel, nothing carried from step to step
+            mixed = ws.get("attn.conv", (T, qn + 2 * kn), ctx.dtype)
+            ops.conv_silu(qkv, mixed, self.w_conv, None, ws.get("attn.no_state", (1, 1), torch.float32), ctx.token_seg,
+                          ctx.seg_slot, ctx.seg_q_start, activation=False)
+            qkv = mixed
         q = ws.get("attn.q", (T, qn), ctx.dtype)
         table = ctx.block_tables[cache.block_table_index]
         cos_sin = self.position.table(ctx.device, ctx.max_positions)

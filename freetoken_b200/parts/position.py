@@ -54,7 +54,8 @@ def scaled_frequencies(rotary_dim: int, theta: float, scaling: Mapping[str, Any]
     if kind == "llama3":
         low, high = float(scaling["low"]), float(scaling["high"])
         wavelength = 2.0 * math.pi / f
-        s = (original / wavelength - low) / (high - low)
+        # high == low leaves no wavelength between the two bounds: the blend is then never chosen
+        s = (original / wavelength - low) / (high - low if high != low else 1.0)
         blended = (1.0 - s) * f / factor + s * f
         out = torch.where(wavelength < original / high, f, torch.where(wavelength > original / low, f / factor, blended))
         return out, 1.0

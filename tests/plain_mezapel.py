@@ -103,7 +103,9 @@ def llama3_frequencies(base, dims, s):
         elif wavelength > original / low:
             out.append(f / factor)
         else:
-            t = (original / wavelength - low) / (high - low)
+            # only reached with high > low: with equal bounds a wavelength is on one side or the other
+            # (one that lies exactly on the bound is divided by the factor here)
+            t = (original / wavelength - low) / (high - low) if high != low else 0.0
             out.append((1.0 - t) * f / factor + t * f)
     return out, 1.0
 

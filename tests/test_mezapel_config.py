@@ -133,7 +133,7 @@ def _broken(path, value):
     (("layers",), []), (("layers", 0, "type"), "attention_3"), (("layers", 0, "mixer", "heads"), None),
     (("layers", 0, "mixer", "kv_heads"), 3), (("layers", 0, "mixer", "scale"), None),
     (("layers", 0, "mixer", "rot", "dims"), 7), (("layers", 0, "mixer", "rot", "dims"), 14),
-    (("layers", 0, "mixer", "rot", "scaling", "fast"), None), (("layers", 1, "mixer", "rot", "scaling", "high"), 1.0),
+    (("layers", 0, "mixer", "rot", "scaling", "fast"), None), (("layers", 1, "mixer", "rot", "scaling", "high"), 0.0),
     (("layers", 1, "mixer", "rot", "scaling", "factor"), 0.0), (("layers", 0, "mlp", "kind"), "moe"),
     (("layers", 0, "mlp", "ff"), None), (("loop", "stop"), 9), (("loop", "times"), 0),
     (("embedding", "bigram", "buckets"), 0), (("embedding", "bigram", "mul_cur"), None),

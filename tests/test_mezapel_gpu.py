@@ -232,6 +232,7 @@ ALONE = {
     "attention_2_no_convolution_no_cap": mz.one_layer(mz.attention_2(3, 1, 20, 20, 11, 8, 0), streams=4),
     "attention_2_window_of_one_long_convolution": mz.one_layer(mz.attention_2(2, 2, 10, 4, 1, 10, 6, softcap=1.0), streams=2),
     "attention_2_window_longer_than_the_sequence": mz.one_layer(mz.attention_2(5, 1, 6, 14, 400, 2, 2, softcap=100.0, scaling=mz.llama3(2.0, 8, 0.5, 3.0)), streams=1),
+    "attention_2_one_tap_equal_bounds_of_the_scaling": mz.one_layer(mz.attention_2(2, 1, 12, 12, 6, 8, 1, scaling=mz.llama3(4.0, 16, 2.0, 2.0)), streams=2),
     "attention_2_nine_taps": mz.one_layer(mz.attention_2(1, 1, 16, 16, 7, 16, 9), streams=2),
     "dense_feed_forward": mz.one_layer(mz.attention(1, 1, 4, 4, 3, 2, mlp=mz.dense(40))),
     "plain_residual_no_second_table": mz.one_layer(mz.attention_2(2, 1, 8, 8, 4, 4, 2, mlp=mz.dense(24)), streams=None, bigram=None),
