@@ -365,8 +365,8 @@ def test_a_far_key_decides(tmp_path, kind, dtype):
     rounded input and come out up to 0.08 off whatever computes them (which is also why the
     vocabulary is a quarter of the width here, and why the value is not simply made larger); with
     the softmax whose sink is only 1, where a token's own value keeps much of the weight, that shows
-    as an error of up to 0.18 at some tokens, so the bound there is 0.2 - a fifth of what losing the
-    far key costs."""
+    as an error of up to 0.18 at some tokens, so the bound there is 0.2 - less than a third of what
+    losing the far key costs."""
     size = 512 if kind == "attention" else 500
     config = mz.one_layer(edge_layer(kind, 16, 12, size), vocab=12, width=48, streams=2, bigram=None)
     state = mz.random_state(config, 43)
@@ -383,7 +383,7 @@ def test_a_far_key_decides(tmp_path, kind, dtype):
     other = list(reqs["t16"])
     other[16] = stand_in
     tol = 0.2 if (kind, dtype) == ("attention", "bfloat16") else mz.TOL[dtype]
-    assert float(mz.position_errors(plain.forward(config, state, other)[-1:], want["t16"][-1:])) > max(0.2, 4 * tol)
+    assert float(mz.position_errors(plain.forward(config, state, other)[-1:], want["t16"][-1:])) > max(0.2, 3 * tol)
     folder = mz.write(str(tmp_path / "m"), config, state)
     for cut in ("decode_tail", "portions", "mixed"):
         schedule = CUTS[cut](reqs)
