@@ -200,7 +200,7 @@ def attn_prefill_tc_window():
     i32 = lambda xs: torch.tensor(xs, dtype=torch.int32, device=DEV)
     tiles = list(range(0, T, 64))
     lists = (i32([0] * len(tiles)), i32(tiles), i32([0, T]), i32([0]))
-    options = ops.ScoreOptions(softcap=30.0, sink=torch.randn(NQ, device=DEV))
+    options = ops.ScoreOptions(softcap=50.0, sink=torch.randn(NQ, device=DEV))
 
     def run(i):
         ops.attn_prefill_tc(q, out, kv[0], *lists, table, NQ, NKV, D, D ** -0.5, window, options=options)

@@ -41,13 +41,13 @@ def mezapel_config(s: Dict[str, int]) -> Dict[str, Any]:
     d = s["dim"]
     chunked = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5,
                "mask": {"size": s["chunk"]},
-               "rot": {"base": 250000.0, "dims": d // 2, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+               "rot": {"base": 10000.0, "dims": d // 2, "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}
     windowed = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5,
-                "mask": {"size": s["window"]}, "conv": TAPS, "softcap": 30.0,
-                "rot": {"base": 1e6, "dims": d, "scaling": {"factor": 8.0, "original": 8192, "low": 1.0, "high": 4.0}}}
+                "mask": {"size": s["window"]}, "conv": TAPS, "softcap": 50.0,
+                "rot": {"base": 500000.0, "dims": d, "scaling": {"factor": 16.0, "original": 8192, "low": 1.0, "high": 8.0}}}
     mlp = {"kind": "dense", "ff": s["ff"] * 2 // 3 // 128 * 128}
     return {"architecture": "Mezapel", "vocab": s["vocab"], "width": s["width"], "streams": s["streams"],
-            "norm": {"eps": 1e-5},
+            "norm": {"eps": 1e-6},
             "embedding": {"scale": float(s["width"]) ** 0.5, "bigram": {"buckets": s["buckets"], "mul_prev": 36313, "mul_cur": 27191}},
             "layers": [{"type": "attention", "mixer": chunked, "mlp": mlp}, {"type": "attention_2", "mixer": windowed, "mlp": mlp},
                        {"type": "attention_2", "mixer": windowed, "mlp": mlp}, {"type": "attention", "mixer": chunked, "mlp": mlp}]}
@@ -149,7 +149,7 @@ def kernel_pairs(s: Dict[str, int], peaks: Dict[str, Any], reps: int = 10) -> Di
     sink = torch.randn(H, device=dev)
     keys = s["window"]
     variants = (("chunks of %d, a sink of score 0" % s["chunk"], None, ops.ScoreOptions(chunk=s["chunk"], sink_value=0.0)),
-                ("a window of %d, capped scores, a learned sink" % s["window"], s["window"], ops.ScoreOptions(softcap=30.0, sink=sink)),
+                ("a window of %d, capped scores, a learned sink" % s["window"], s["window"], ops.ScoreOptions(softcap=50.0, sink=sink)),
                 ("a window of %d, plain" % s["window"], s["window"], None))
     for label, window, options in variants:
         run(f"attn_decode, 64 x 2,048 keys, {label}",
@@ -174,7 +174,7 @@ def kernel_pairs(s: Dict[str, int], peaks: Dict[str, Any], reps: int = 10) -> Di
     pairs_chunk = sum(i % s["chunk"] + 1 for i in range(T))
     for label, window, options, pairs in (
             ("chunks of %d, a sink of score 0" % s["chunk"], None, ops.ScoreOptions(chunk=s["chunk"], sink_value=0.0), pairs_chunk),
-            ("a window of %d, capped scores, a learned sink" % w, w, ops.ScoreOptions(softcap=30.0, sink=sink), pairs_window),
+            ("a window of %d, capped scores, a learned sink" % w, w, ops.ScoreOptions(softcap=50.0, sink=sink), pairs_window),
             ("a window of %d, a learned sink" % w, w, ops.ScoreOptions(sink=sink), pairs_window),
             ("a window of %d, plain" % w, w, None, pairs_window)):
         run(f"attn_prefill (mma.sync), 8,192 tokens, {label}",

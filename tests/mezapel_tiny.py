@@ -21,11 +21,11 @@ from fazinex_tiny import make_engine, position_errors, tokens, write_model  # no
 from tonapel_tiny import compare  # noqa: F401  (re-exported)
 
 
-def yarn(factor, original, fast=32.0, slow=1.0):
+def yarn(factor, original, fast=24.0, slow=1.5):
     return {"factor": factor, "original": original, "fast": fast, "slow": slow}
 
 
-def llama3(factor, original, low=1.0, high=4.0):
+def llama3(factor, original, low=0.5, high=3.0):
     return {"factor": factor, "original": original, "low": low, "high": high}
 
 
@@ -72,7 +72,7 @@ def model(vocab, width, streams, eps, layers, scale=1.0, bigram=None, loop=None)
 # feed-forward; value heads wider and narrower than key heads; the loop covers the middle
 MZ_A: Dict = model(150, 40, 2, 1e-5, [
     attention(4, 2, 12, 10, 7, 6, base=100.0, scaling=yarn(4.0, 16), mlp=dense(56)),
-    attention_2(3, 3, 10, 14, 5, 10, 2, softcap=5.0, base=300.0, scaling=llama3(8.0, 32, 1.0, 2.0), mlp=dense(24)),
+    attention_2(3, 3, 10, 14, 5, 10, 2, softcap=5.0, base=300.0, scaling=llama3(7.0, 32, 1.0, 2.0), mlp=dense(24)),
     attention(2, 1, 6, 6, 1, 0),
     attention_2(6, 2, 14, 6, 9, 4, 4, scale=0.4, mlp=dense(30)),
 ], scale=3.0, bigram=(37, 11, 5), loop=(1, 3, 2))
@@ -80,12 +80,12 @@ MZ_A: Dict = model(150, 40, 2, 1e-5, [
 # sizes the tensor-core attention kernels take (heads of 64 and 128 values), pages of 64, chunks and windows
 # shorter than, equal to and longer than a page; four streams; the loop covers the first layer
 MZ_B: Dict = model(320, 128, 4, 2e-6, [
-    attention(4, 2, 64, 64, 100, 32, base=500000.0, scaling=yarn(8.0, 64), mlp=dense(256)),
-    attention_2(8, 2, 128, 128, 64, 128, 4, softcap=20.0, base=1e6, scaling=llama3(8.0, 128), mlp=dense(192)),
+    attention(4, 2, 64, 64, 100, 32, base=500000.0, scaling=yarn(5.0, 64), mlp=dense(256)),
+    attention_2(8, 2, 128, 128, 64, 128, 4, softcap=20.0, base=3e6, scaling=llama3(6.0, 128), mlp=dense(192)),
     attention(2, 2, 128, 64, 64, 64, base=5000.0, scale=0.15),
     attention_2(4, 1, 64, 32, 130, 16, 3, base=30000.0, mlp=dense(128)),
     attention(8, 1, 32, 32, 33, 32, base=777.0, scaling=yarn(2.0, 40, fast=8.0, slow=2.0), mlp=dense(64)),
-], scale=11.3, bigram=(509 * 2 + 1, 31, 7), loop=(0, 1, 3))
+], scale=11.3, bigram=(1021, 31, 7), loop=(0, 1, 3))
 
 # one stream with connection weights; no hashed table; no convolution in one layer; a width that is no
 # multiple of 4; the loop covers everything

@@ -183,7 +183,7 @@ def test_plain_masks_and_sinks():
 
 
 def test_plain_loop_repeats_the_range_as_a_whole():
-    assert plain.run_order({"layers": [0] * 5, "loop": {"start": 1, "stop": 3, "times": 3}}) == [0, 1, 2, 1, 2, 1, 2, 3, 4]
+    assert plain.run_order({"layers": [0] * 5, "loop": {"start": 2, "stop": 4, "times": 2}}) == [0, 1, 2, 3, 2, 3, 4]
     assert plain.run_order({"layers": [0] * 2}) == [0, 1]
     cfg = MezapelConfig.from_dict(mz.MZ_B)
     assert cfg.run_order() == plain.run_order(mz.MZ_B)
