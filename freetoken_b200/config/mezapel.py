@@ -12,7 +12,7 @@ attention with a sigmoid gate read from the mixer's input:
 
 * ``attention``: RMS norm over the whole q and the whole k projection, the first ``rot.dims``
   dimensions of a head rotated in halves with YaRN-scaled frequencies, a mask in chunks of
-  ``mask.size`` positions, a softmax whose denominator has one added (a sink of score 0), one gate
+  ``mask.size`` positions, softmax weights ``e^s / (1 + sum e^s)`` (a sink of score 0), one gate
   per head;
 * ``attention_2``: a causal convolution of ``conv`` taps behind each of q, k and v, RMS norm per
   head with a weight the heads share, Llama-3.1-scaled frequencies, scores capped by ``softcap *
@@ -42,7 +42,7 @@ ARCHITECTURE = "Mezapel"
 MIXER_TYPES = ("attention", "attention_2")
 MLP_KINDS = ("dense",)
 # constants the design fixes
-ZERO_SINK_SCORE = 0.0            # "one added to the denominator" is a sink whose score is 0
+ZERO_SINK_SCORE = 0.0            # a denominator of 1 + sum(e^s) is that of a sink with the score 0
 SCALING_OF = {"attention": "yarn", "attention_2": "llama3"}     # which rule a mixer's rot.scaling follows
 SCALING_KEYS = {"yarn": ("factor", "original", "fast", "slow"), "llama3": ("factor", "original", "low", "high")}
 MAX_STREAMS = 8                  # what the stream kernel keeps in registers

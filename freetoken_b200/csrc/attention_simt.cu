@@ -13,7 +13,7 @@
 // q.k * scale for keys j <= pos (and j > pos - window when a window is set),
 // softmax over them, weighted sum of v; query head h reads KV head h / group.
 // Options no model of the reference has: a mask in chunks (a query sees the keys
-// of its own chunk of `chunk` positions, counted from position 0), scores capped
+// of its own chunk: floor(j / chunk) == floor(pos / chunk)), scores capped
 // as cap * tanh(s / cap), and a sink - a score without key or value that enters
 // the softmax's denominator only, fixed (sink_mode 1) or one per query head (2).
 #include "common.cuh"

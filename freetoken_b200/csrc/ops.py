@@ -941,8 +941,8 @@ def pass_rows(rows: int) -> int:
 # ------------------------------------------------------------- attention
 class ScoreOptions:
     """What a softmax attention may do to its scores beyond scale and window, as every attention
-    kernel takes it: ``chunk`` (> 0: a query sees the keys of its own chunk of that many positions,
-    counted from position 0), ``softcap`` (> 0: ``s <- softcap * tanh(s / softcap)``), and a sink -
+    kernel takes it: ``chunk`` (> 0: a query at ``p`` sees the keys ``j`` with ``floor(j / chunk) ==
+    floor(p / chunk)``), ``softcap`` (> 0: ``s <- softcap * tanh(s / softcap)``), and a sink -
     a score without key or value that enters the softmax's denominator only: ``sink_value`` (a
     fixed score) or ``sink`` (float32, one learned score per query head)."""
 

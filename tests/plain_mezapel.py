@@ -8,8 +8,8 @@ dictionary, ``w`` a dictionary of tensors by checkpoint name.
 * embedding: the token's row times a scale plus a row of a second table chosen by a hash of the
   token and the one before it (a row of its own for a sequence's first token);
 * residual: a plain pre-norm sum, or ``streams`` copies joined by hyper-connections;
-* mixers: ``attention`` (query/key norm over the whole projection, a rotated part with YaRN
-  frequencies, a mask in chunks, a softmax whose denominator has one added, a gate per head) and
+* mixers: ``attention`` (one norm over all of q and one over all of k, a rotated part with YaRN
+  frequencies, a mask in chunks, softmax weights ``e^s / (1 + sum e^s)``, a gate per head) and
   ``attention_2`` (short convolutions behind the projections, a norm per head, Llama-3.1
   frequencies, capped scores, a sliding window, a learned sink per head, a gate per value);
 * feed-forward: ``W_down (silu(W_gate h) (W_up h))``.
@@ -147,7 +147,7 @@ def masked_softmax_with_sink(scores, visible, sink):
 
 def attention(h, w, p, m, eps):
     """Mixer ``attention``: norm over all of q and all of k, part of each head rotated with YaRN
-    frequencies, keys of the query's own chunk only, one added to the softmax's denominator, a
+    frequencies, keys of the query's own chunk only, softmax weights ``e^s / (1 + sum e^s)``, a
     sigmoid gate per head."""
     T = h.shape[0]
     H, G, D, V = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
