@@ -146,6 +146,9 @@ OPTION_CASES = [
     (3, 1, 64, 64, [(30, 260), (0, 2)], None, 96, 6.0, "zero"),                             # chunks across tiles; three heads a key head
     (2, 2, 128, 128, [(250, 200)], 64, None, 0.0, None),                                     # a window of one tile, nothing else
     (4, 1, 64, 64, [(1000, 150), (64, 64)], None, 512, 25.0, "learned"),
+    (2, 1, 64, 64, [(0, 130), (200, 1)], 1, None, 0.0, "learned"),                           # a window of one: only the sink beside the key itself
+    (2, 2, 128, 64, [(60, 70), (129, 1)], None, 1, 5.0, "zero"),
+    (24, 1, 64, 64, [(300, 1), (10, 66)], 150, None, 0.0, "learned"),                        # 24 heads a key head: two head tiles in decoding
 ]
 
 
