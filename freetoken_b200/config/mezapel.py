@@ -211,6 +211,7 @@ def _mixer_spec(cfg: MezapelConfig, layer: MezapelLayer) -> PartSpec:
     params: Dict[str, Any] = {
         "hidden_size": cfg.width, "num_heads": m.heads, "num_kv_heads": m.kv_heads, "head_dim": m.dim,
         "value_dim": m.vdim, "sm_scale": m.scale, "qk_norm_eps": cfg.norm_eps, "position": position, "scope": "mix",
+        "fill_heads": True,
         "checkpoint_names": {"q": "q", "k": "k", "v": "v", "o": "o", "qkv": "qkvg", "q_norm": "q.norm",
                              "k_norm": "k.norm", "gate": "g", "sink": "sink", "q_conv": "q.conv",
                              "k_conv": "k.conv", "v_conv": "v.conv", "qkv_conv": "qkv.conv"}}

@@ -88,11 +88,12 @@ class PagedSoftmaxCore:
         }
         return StepPlan(arrays=arrays, host=host)
 
-    def attention_libraries(self, dtype) -> List[str]:
+    def attention_libraries(self, dtype, d: int = 0) -> List[str]:
+        d = d or self.d
         fast = []
-        if dtype == torch.bfloat16 and self.d in ops.DECODE_HEAD_DIMS:
+        if dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS:
             fast = ["attention_decode", "attention_prefill"]
-        if fast and self.d in (64, 128):
+        if fast and d in (64, 128):
             # TMA-fed kernels (the prefill one also builds the tensor maps both use)
             fast += ["attention_prefill_tc", "attention_decode_tma"]
         return ["attention_simt"] + fast
@@ -149,7 +150,12 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
     tanh(score / cap)``.  ``sink_value`` (a fixed score) or ``sink`` (True: a learned score per
     head, ``checkpoint_names`` sink): a score without key or value in the softmax's denominator.
     ``gate`` (``"head"`` or ``"element"``): the heads' outputs times ``sigmoid(Wg x)``, one gate
-    per head or per value (``checkpoint_names`` gate), merged into the qkv product."""
+    per head or per value (``checkpoint_names`` gate), merged into the qkv product.
+    ``fill_heads`` (default False): in bfloat16, heads of up to 128 values that are no size of the
+    tensor-core attention kernels (32, 64, 128) are filled up with zeros to the next one, exactly as
+    heads are filled up to the larger of key and value size: a model with heads of 96 values then
+    runs its prompts and decoded tokens on the tensor-core kernels with heads of 128, at the price
+    of a third more cache and arithmetic in the mixer.  float32 keeps the sizes as they are."""
 
     graph_capturable = True
     writes_into_out = True
@@ -162,7 +168,8 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
         self.nkv = int(p["num_kv_heads"])
         self.dk = int(p["head_dim"])
         self.dv = int(p.get("value_dim") or self.dk)
-        self.d = max(self.dk, self.dv)          # the head size the kernels and the cache see
+        self.d = max(self.dk, self.dv)          # the head size the kernels and the cache see (bind may fill it up)
+        self.fill_heads = bool(p.get("fill_heads", False))
         self.has_bias = bool(p.get("bias", False))
         self.scale = float(p["sm_scale"])
         self.norm_mode = _NORM_MODES[p.get("qk_norm", "none")]
@@ -271,7 +278,15 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
             pieces.append(torch.cat((run, run.new_zeros(pad)), axis + 1).flatten(axis, axis + 1))
         return torch.cat(pieces, axis).contiguous()
 
+    def _head_size(self, dtype) -> int:
+        """The head size the kernels and the cache see for compute dtype ``dtype``."""
+        d = max(self.dk, self.dv)
+        if self.fill_heads and dtype == torch.bfloat16 and d <= max(ops.DECODE_HEAD_DIMS):
+            return min(size for size in ops.DECODE_HEAD_DIMS if size >= d)
+        return d
+
     def bind(self, tensors: Dict[str, torch.Tensor], dtype) -> None:
+        self.d = self._head_size(dtype)
         runs = ((self.nq, self.dk), (self.nkv, self.dk), (self.nkv, self.dv))
         gate_runs = () if not self.gate else (((self.nq, 1),) if self.gate == "head" else ((self.nq, self.dv),))
         if self.gate == "head":
@@ -298,7 +313,7 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
             self.options = ops.ScoreOptions(self.chunk, self.softcap, self.sink_value, self.w_sink)
 
     def libraries(self, dtype) -> List[str]:
-        return (["elementwise"] + self.attention_libraries(dtype) + linear.libraries(dtype, self.has_bias)
+        return (["elementwise"] + self.attention_libraries(dtype, self._head_size(dtype)) + linear.libraries(dtype, self.has_bias)
                 + (["recurrent"] if self.taps else []) + (["rowwise"] if self.gate else []))
 
     # ---- forward ----------------------------------------------------------------

@@ -54,6 +54,7 @@ def test_plan_hands_every_constant_to_a_part(which):
         m, p = layer["mixer"], spec.mixer.params
         assert (p["num_heads"], p["num_kv_heads"], p["head_dim"], p["value_dim"], p["sm_scale"], p["qk_norm_eps"]) == \
             (m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["scale"], raw["norm"]["eps"])
+        assert p["fill_heads"] is True
         pos = p["position"]
         assert (pos.kind, pos.params["rotary_dim"], pos.params["theta"]) == ("rotary_neox", m["rot"]["dims"], m["rot"]["base"])
         scaling = m["rot"].get("scaling") if m["rot"]["dims"] else None

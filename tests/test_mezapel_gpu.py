@@ -488,3 +488,37 @@ def test_trace_replay_tool(models, tmp_path, dtype):
                             rd.peak_tokens(schedule, page), page, mz.MZ[which]["vocab"])
     want = {rid: plain.forward(mz.MZ[which], state, toks) for rid, toks in reqs.items()}
     mz.compare(got, want, mz.TOL[dtype], f"trace_run, mixed [{dtype}]")
+
+
+# ------------------------------------------- heads of sizes the tensor-core kernels do not take
+FILLED = mz.model(200, 160, 2, 1e-5, [
+    mz.attention(4, 2, 80, 48, 300, 40, base=20000.0, scaling=mz.yarn(4.0, 128), mlp=mz.dense(256)),
+    mz.attention_2(4, 1, 40, 72, 90, 40, 3, softcap=25.0, scaling=mz.llama3(4.0, 256), mlp=mz.dense(192)),
+], scale=12.0, bigram=(251, 13, 29))
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_heads_of_other_sizes_are_filled_up_for_the_tensor_core_kernels(tmp_path, monkeypatch, dtype):
+    """Heads of 80 (keys) and 48 (values), of 40 and 72: in bfloat16 the mixer fills them up to 128 and
+    runs prompts on the tcgen05 and mma.sync kernels and decoded tokens on the split-KV kernel; the norm
+    over q and k still counts the real values only.  float32 keeps heads of 80 and 72 on the generic kernel."""
+    from freetoken_b200.csrc import ops
+    calls = {"prefill": 0, "prefill_tc": 0, "decode": 0, "generic": 0}
+    for name, fn in (("prefill", "attn_prefill"), ("prefill_tc", "attn_prefill_tc"), ("decode", "attn_decode"),
+                     ("generic", "attn_paged_simt")):
+        real = getattr(ops, fn)
+        monkeypatch.setattr(ops, fn, lambda *a, _n=name, _r=real, **k: (calls.__setitem__(_n, calls[_n] + 1), _r(*a, **k))[1])
+    state = mz.random_state(FILLED, 9)
+    folder = mz.write(str(tmp_path / "m"), FILLED, state)
+    reqs = {f"r{i}": mz.tokens(17 * i + 1, n, FILLED["vocab"]) for i, n in enumerate([700, 130, 64, 3])}
+    want = {rid: plain.forward(FILLED, state, toks) for rid, toks in reqs.items()}
+    for cut in ("whole", "mixed"):
+        schedule = CUTS[cut](reqs)
+        engine = mz.make_engine(folder, dtype, 64, rd.peak_tokens(schedule, 64), poison=True)
+        sizes = [b.mixer.d for b in engine.model.blocks]
+        assert sizes == ([128, 128] if dtype == "bfloat16" else [80, 72])
+        mz.compare(rd.run_engine(engine, reqs, schedule), want, mz.TOL[dtype], f"filled heads, {cut} [{dtype}]")
+    if dtype == "bfloat16":
+        assert calls["generic"] == 0 and min(calls["prefill"], calls["prefill_tc"], calls["decode"]) > 0, calls
+    else:
+        assert calls["generic"] > 0 and calls["prefill"] + calls["prefill_tc"] + calls["decode"] == 0, calls
