@@ -153,9 +153,9 @@ class PagedAttention(PagedSoftmaxCore, Mixer):
     per head or per value (``checkpoint_names`` gate), merged into the qkv product.
     ``fill_heads`` (default False): in bfloat16, heads of up to 128 values that are no size of the
     tensor-core attention kernels (32, 64, 128) are filled up with zeros to the next one, exactly as
-    heads are filled up to the larger of key and value size: a model with heads of 96 values then
+    heads are filled up to the larger of key and value size: a model with heads of 112 values then
     runs its prompts and decoded tokens on the tensor-core kernels with heads of 128, at the price
-    of a third more cache and arithmetic in the mixer.  float32 keeps the sizes as they are."""
+    of a seventh more cache and arithmetic in the mixer.  float32 keeps the sizes as they are."""
 
     graph_capturable = True
     writes_into_out = True
